@@ -87,8 +87,9 @@ def bytes_per_page(cache_specs, cache_from, page_size, dtype):
 
 
 class CacheStorage:
-    def __init__(self, cache_specs, cache_from, page_size, pages_per_group, max_requests, dtype, device):
-        """pages_per_group: int (same for every group) or {group: int}."""
+    def __init__(self, cache_specs, cache_from, page_size, pages_per_group, max_requests, dtype, device, embedding_spec=None):
+        """pages_per_group: int (same for every group) or {group: int}.  ``embedding_spec``: a StateSpec for what the
+        model's embedding keeps per request slot (None: nothing); its storage is ``self.embedding``."""
         groups, self.layer_group = plan_groups(cache_specs, cache_from)
         if isinstance(pages_per_group, int):
             pages_per_group = {g: pages_per_group for g in groups}
@@ -107,6 +108,7 @@ class CacheStorage:
             if src is not None:
                 s = self.layers[src]
                 self.layers[i] = LayerCache(s.group, page_size, kv=s.kv, state=s.state, writable=False)
+        self.embedding = None if embedding_spec is None else self._make(embedding_spec, "the embedding", pages_per_group)
 
     def _make(self, spec, what, pages_per_group):
         page_size = self.page_size

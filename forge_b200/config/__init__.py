@@ -2,6 +2,7 @@ from .base import ConfigError, LayerSpec, ModelPlan, PartSpec
 from .llama import LlamaConfig
 from .zatupel import ZatupelConfig
 from .tidenex import TidenexConfig
+from .tuzavik import TuzavikConfig
 from .registry import (config_from_dict, load_config, register_architecture, registered_architectures,
                        unregister_architecture)
 
@@ -16,5 +17,9 @@ register_architecture("Zatupel", ZatupelConfig, replace=True)
 # pre-norm layers of differential attention, or of an attention beside a gated linear recurrence; a span of layers may repeat
 register_architecture("Tidenex", TidenexConfig, replace=True)
 
-__all__ = ["ZatupelConfig", "TidenexConfig", "ConfigError", "LayerSpec", "ModelPlan", "PartSpec", "LlamaConfig", "config_from_dict", "load_config",
+# layers of retention or of attention over one cached latent per token, every sublayer's output normed before it joins the stream,
+# dense or routed feed-forwards, an embedding that also looks at the token before
+register_architecture("Tuzavik", TuzavikConfig, replace=True)
+
+__all__ = ["ZatupelConfig", "TidenexConfig", "TuzavikConfig", "ConfigError", "LayerSpec", "ModelPlan", "PartSpec", "LlamaConfig", "config_from_dict", "load_config",
            "register_architecture", "registered_architectures", "unregister_architecture"]

@@ -23,7 +23,8 @@ class LayerSpec:
 
     ``cache_from``: index (into ``ModelPlan.layers``) of another layer whose cache this layer's mixer
     reads instead of keeping one of its own.  ``norm_prefixes``: what the names of each norm's tensors start with
-    (None: the block arrangement's own).
+    (None: the block arrangement's own).  ``block_params``: numbers of the arrangement itself (a factor on what joins the
+    stream, say).
     """
     block: str
     mixer: PartSpec
@@ -32,6 +33,7 @@ class LayerSpec:
     weight_prefix: str
     cache_from: Optional[int] = None
     norm_prefixes: Optional[Dict[str, str]] = None
+    block_params: Optional[Dict[str, Any]] = None
 
 
 @dataclass(frozen=True)

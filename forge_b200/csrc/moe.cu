@@ -1,0 +1,270 @@
+// A feed-forward made of many small gated feed-forwards ("experts") of which a router picks a few per token.
+//
+//   route       z = Wr x in fp32, score = sigmoid(z) (or softmax over the experts), the `top` largest scores (the lower index
+//               wins a tie) are the token's experts and, as they are or divided by their sum, its weights
+//   by pairs    every (token, chosen expert) pair on its own: act = act_fn(Wg_e x) * (Wu_e x), then for every token
+//               y = sum over its experts, in the order the router chose them, of weight * Wd_e act.  Everything is read from
+//               device memory, so the path can be replayed in a CUDA graph; it is the path of steps with few tokens
+//   sorted      for steps of many tokens: the pairs are ranked by (expert, token) so that each expert's tokens are
+//               consecutive rows, the rows go through ordinary matrix products expert by expert, and a last kernel adds a
+//               token's experts up in the router's order
+//
+// Router arithmetic is fp32 whatever the activations' type.  Every sum has a fixed order: a dot product is dealt to the
+// lanes of a warp by index and summed by the butterfly, a token's experts are added in the order of their scores.
+#include "common.cuh"
+
+namespace {
+
+__device__ __forceinline__ float sigmoidf(float x) { return 1.0f / (1.0f + expf(-x)); }
+__device__ __forceinline__ float siluf(float x) { return x * sigmoidf(x); }
+
+// A warp per token.  scores in shared memory, [warp][E].
+template <typename TA>
+__global__ void __launch_bounds__(128)
+moe_route_kernel(const TA* __restrict__ x, const float* __restrict__ Wr, int32_t* __restrict__ idx, float* __restrict__ wts, int T,
+                 int W, int E, int top, int softmax, int renorm) {
+    extern __shared__ float sc[];
+    forge::pdl_launch_dependents();
+    forge::pdl_wait();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, t = blockIdx.x * 4 + warp;
+    if (t >= T) return;
+    float* s = sc + warp * E;
+    const TA* xr = x + (size_t)t * W;
+    for (int e = 0; e < E; ++e) {
+        const float* w = Wr + (size_t)e * W;
+        float a = 0.f;
+        for (int c = lane; c < W; c += 32) a = fmaf(forge::to_float(xr[c]), w[c], a);
+        a = forge::warp_sum(a);
+        if (lane == 0) s[e] = a;
+    }
+    __syncwarp();
+    if (lane == 0) {
+        if (softmax) {
+            float m = -INFINITY, sum = 0.f;
+            for (int e = 0; e < E; ++e) m = fmaxf(m, s[e]);
+            for (int e = 0; e < E; ++e) { s[e] = expf(s[e] - m); sum += s[e]; }
+            for (int e = 0; e < E; ++e) s[e] /= sum;
+        } else {
+            for (int e = 0; e < E; ++e) s[e] = sigmoidf(s[e]);
+        }
+        float total = 0.f;
+        for (int k = 0; k < top; ++k) {
+            int best = 0;
+            float bv = -INFINITY;
+            for (int e = 0; e < E; ++e)
+                if (s[e] > bv) { bv = s[e]; best = e; }
+            idx[(size_t)t * top + k] = best;
+            wts[(size_t)t * top + k] = bv;
+            total += bv;
+            s[best] = -INFINITY;
+        }
+        if (renorm)
+            for (int k = 0; k < top; ++k) wts[(size_t)t * top + k] /= total;
+    }
+}
+
+// dot of a weight row (global) with a vector in shared memory, dealt to the lanes by index; the same order whatever the type
+template <typename TW>
+__device__ __forceinline__ float lane_dot(const TW* __restrict__ w, const float* __restrict__ xs, int n, int lane) {
+    float a = 0.f;
+    for (int c = lane; c < n; c += 32) a = fmaf(forge::to_float(w[c]), xs[c], a);
+    return a;
+}
+template <>
+__device__ __forceinline__ float lane_dot<__nv_bfloat16>(const __nv_bfloat16* __restrict__ w, const float* __restrict__ xs, int n, int lane) {
+    float a = 0.f;
+    if ((n & 7) == 0 && (((uintptr_t)w) & 15) == 0) {
+        for (int c = lane * 8; c < n; c += 256) {
+            const uint4 raw = *reinterpret_cast<const uint4*>(w + c);
+            const __nv_bfloat162* p = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const float2 f = __bfloat1622float2(p[i]);
+                a = fmaf(f.x, xs[c + 2 * i], a);
+                a = fmaf(f.y, xs[c + 2 * i + 1], a);
+            }
+        }
+        return a;
+    }
+    for (int c = lane; c < n; c += 32) a = fmaf(__bfloat162float(w[c]), xs[c], a);
+    return a;
+}
+
+constexpr int kPairOutputs = 32;          // outputs per CTA (8 per warp)
+
+// grid (pairs, ceil(F / 32)): act[pair, j] = act_fn(Wg[e][j] . x) * (Wu[e][j] . x);  row j of expert e lies at (e * F + j) * ld
+// in both (ld = W: two matrices [E, F, W]; ld = 2 W and Wu = Wg + W: one matrix whose rows alternate gate, up).
+template <typename TA, typename TW>
+__global__ void __launch_bounds__(128)
+moe_pair_gate_up_kernel(const TA* __restrict__ x, const TW* __restrict__ Wg, const TW* __restrict__ Wu, const int32_t* __restrict__ idx,
+                        TA* __restrict__ act, int W, int F, int top, long long ld) {
+    extern __shared__ float xs[];
+    forge::pdl_launch_dependents();
+    forge::pdl_wait();
+    const int p = blockIdx.x, t = p / top, e = idx[p];
+    for (int c = threadIdx.x; c < W; c += 128) xs[c] = forge::to_float(x[(size_t)t * W + c]);
+    __syncthreads();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    for (int jj = 0; jj < kPairOutputs / 4; ++jj) {
+        const int j = blockIdx.y * kPairOutputs + warp * (kPairOutputs / 4) + jj;
+        if (j >= F) break;
+        const size_t row = ((size_t)e * F + j) * ld;
+        const float g = forge::warp_sum(lane_dot(Wg + row, xs, W, lane));
+        const float u = forge::warp_sum(lane_dot(Wu + row, xs, W, lane));
+        if (lane == 0) act[(size_t)p * F + j] = forge::from_float<TA>(siluf(g) * u);
+    }
+}
+
+// grid (T, ceil(Wd / 32)): y[t, n] = sum_k wts[t, k] * (Wd[e_k][n] . act[(t, k)]);  Wd [E, W, F].
+template <typename TA, typename TW>
+__global__ void __launch_bounds__(128)
+moe_pair_down_kernel(const TA* __restrict__ act, const TW* __restrict__ Wd, const int32_t* __restrict__ idx, const float* __restrict__ wts,
+                     float* __restrict__ y, int W, int F, int top) {
+    extern __shared__ float as[];             // [top][F]
+    forge::pdl_launch_dependents();
+    forge::pdl_wait();
+    const int t = blockIdx.x;
+    for (int i = threadIdx.x; i < top * F; i += 128) as[i] = forge::to_float(act[(size_t)t * top * F + i]);
+    __syncthreads();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    for (int nn = 0; nn < kPairOutputs / 4; ++nn) {
+        const int n = blockIdx.y * kPairOutputs + warp * (kPairOutputs / 4) + nn;
+        if (n >= W) break;
+        float sum = 0.f;
+        for (int k = 0; k < top; ++k) {
+            const int e = idx[(size_t)t * top + k];
+            const float d = forge::warp_sum(lane_dot(Wd + ((size_t)e * W + n) * F, as + k * F, F, lane));
+            sum = fmaf(wts[(size_t)t * top + k], d, sum);
+        }
+        if (lane == 0) y[(size_t)t * W + n] = sum;
+    }
+}
+
+// One CTA per expert walks all pairs in order: rank[p] = how many earlier pairs chose the same expert; counts[e].
+__global__ void __launch_bounds__(256)
+moe_rank_kernel(const int32_t* __restrict__ idx, int32_t* __restrict__ rank, int32_t* __restrict__ counts, int P) {
+    __shared__ int warp_tot[8];
+    __shared__ int base;
+    forge::pdl_launch_dependents();
+    forge::pdl_wait();
+    const int e = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    if (threadIdx.x == 0) base = 0;
+    __syncthreads();
+    for (int p0 = 0; p0 < P; p0 += 256) {
+        const int p = p0 + threadIdx.x;
+        const bool mine = p < P && idx[p] == e;
+        const unsigned m = __ballot_sync(0xffffffffu, mine);
+        if (lane == 0) warp_tot[warp] = __popc(m);
+        __syncthreads();
+        int before = base;
+        for (int w = 0; w < warp; ++w) before += warp_tot[w];
+        if (mine) rank[p] = before + __popc(m & ((1u << lane) - 1u));
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            int tot = 0;
+            for (int w = 0; w < 8; ++w) tot += warp_tot[w];
+            base += tot;
+        }
+        __syncthreads();
+    }
+    if (threadIdx.x == 0) counts[e] = base;
+}
+
+// One CTA per pair: its row in the sorted order = (pairs of lower experts) + rank; copies the token's input there.
+template <typename TA>
+__global__ void __launch_bounds__(128)
+moe_gather_kernel(const TA* __restrict__ x, const int32_t* __restrict__ idx, const int32_t* __restrict__ rank,
+                  const int32_t* __restrict__ counts, int32_t* __restrict__ dest, TA* __restrict__ xg, int W, int top) {
+    __shared__ int s_dest;
+    forge::pdl_launch_dependents();
+    forge::pdl_wait();
+    const int p = blockIdx.x, t = p / top;
+    if (threadIdx.x == 0) {
+        const int e = idx[p];
+        int off = 0;
+        for (int i = 0; i < e; ++i) off += counts[i];
+        s_dest = off + rank[p];
+        dest[p] = s_dest;
+    }
+    __syncthreads();
+    const TA* src = x + (size_t)t * W;
+    TA* dst = xg + (size_t)s_dest * W;
+    for (int c = threadIdx.x; c < W; c += 128) dst[c] = src[c];
+}
+
+// y[t, :] = sum_k wts[t, k] * ys[dest[t, k], :], k in order.
+__global__ void __launch_bounds__(128)
+moe_combine_kernel(const float* __restrict__ ys, const int32_t* __restrict__ dest, const float* __restrict__ wts, float* __restrict__ y,
+                   int W, int top) {
+    forge::pdl_launch_dependents();
+    forge::pdl_wait();
+    const int t = blockIdx.x;
+    for (int c = threadIdx.x; c < W; c += 128) {
+        float sum = 0.f;
+        for (int k = 0; k < top; ++k) sum = fmaf(wts[(size_t)t * top + k], ys[(size_t)dest[(size_t)t * top + k] * W + c], sum);
+        y[(size_t)t * W + c] = sum;
+    }
+}
+
+}  // namespace
+
+// x [T, W] of type dtype; Wr fp32 [E, W]; idx int32 [T, top]; wts fp32 [T, top].  softmax 0: scores are sigmoids.
+extern "C" int forge_moe_route(const void* x, int dtype, const float* Wr, int32_t* idx, float* wts, int T, int W, int E, int top,
+                               int softmax, int renorm, cudaStream_t stream) {
+    if (T < 0 || W <= 0 || E <= 0 || top <= 0 || top > E) return forge::fail(FORGE_ERR_ARG, "moe_route: bad sizes T=%d W=%d E=%d top=%d", T, W, E, top);
+    if (E > 2048) return forge::fail(FORGE_ERR_UNSUPPORTED, "moe_route: %d experts", E);
+    if (T == 0) return FORGE_OK;
+    cudaError_t e = cudaSuccess;
+    FORGE_DISPATCH_DTYPE(dtype, TT,
+        e = forge::launch(moe_route_kernel<TT>, dim3((T + 3) / 4), dim3(128), sizeof(float) * 4 * E, stream, 1, (const TT*)x, Wr, idx, wts, T, W,
+                          E, top, softmax, renorm));
+    return forge::check_launch("moe_route", e);
+}
+
+// x [T, W], act [T*top, F] of type dtype; Wg, Wu of type dtype, row j of expert e at (e * F + j) * ld elements.
+extern "C" int forge_moe_pair_gate_up(const void* x, const void* Wg, const void* Wu, const int32_t* idx, void* act, int dtype, int T,
+                                      int W, int F, int top, long long ld, cudaStream_t stream) {
+    if (T < 0 || W <= 0 || F <= 0 || top <= 0) return forge::fail(FORGE_ERR_ARG, "moe_pair_gate_up: bad sizes T=%d W=%d F=%d top=%d", T, W, F, top);
+    if (W > 12000) return forge::fail(FORGE_ERR_UNSUPPORTED, "moe_pair_gate_up: rows of %d", W);
+    if (T == 0) return FORGE_OK;
+    cudaError_t e = cudaSuccess;
+    FORGE_DISPATCH_DTYPE(dtype, TT,
+        e = forge::launch(moe_pair_gate_up_kernel<TT, TT>, dim3(T * top, (F + kPairOutputs - 1) / kPairOutputs), dim3(128), sizeof(float) * W,
+                          stream, 1, (const TT*)x, (const TT*)Wg, (const TT*)Wu, idx, (TT*)act, W, F, top, ld));
+    return forge::check_launch("moe_pair_gate_up", e);
+}
+
+// act [T*top, F] of type dtype; Wd [E, W, F] of type dtype; y fp32 [T, W].
+extern "C" int forge_moe_pair_down(const void* act, const void* Wd, const int32_t* idx, const float* wts, float* y, int dtype, int T, int W,
+                                   int F, int top, cudaStream_t stream) {
+    if (T < 0 || W <= 0 || F <= 0 || top <= 0) return forge::fail(FORGE_ERR_ARG, "moe_pair_down: bad sizes T=%d W=%d F=%d top=%d", T, W, F, top);
+    if ((size_t)top * F * sizeof(float) > 48 * 1024) return forge::fail(FORGE_ERR_UNSUPPORTED, "moe_pair_down: %d experts of %d channels a token", top, F);
+    if (T == 0) return FORGE_OK;
+    cudaError_t e = cudaSuccess;
+    FORGE_DISPATCH_DTYPE(dtype, TT,
+        e = forge::launch(moe_pair_down_kernel<TT, TT>, dim3(T, (W + kPairOutputs - 1) / kPairOutputs), dim3(128), sizeof(float) * top * F, stream,
+                          1, (const TT*)act, (const TT*)Wd, idx, wts, y, W, F, top));
+    return forge::check_launch("moe_pair_down", e);
+}
+
+// idx int32 [P]; rank, dest int32 [P]; counts int32 [E]; x [T, W], xg [P, W] of type dtype.
+extern "C" int forge_moe_sort(const void* x, int dtype, const int32_t* idx, int32_t* rank, int32_t* counts, int32_t* dest, void* xg, int T,
+                              int W, int E, int top, cudaStream_t stream) {
+    if (T < 0 || W <= 0 || E <= 0 || top <= 0) return forge::fail(FORGE_ERR_ARG, "moe_sort: bad sizes T=%d W=%d E=%d top=%d", T, W, E, top);
+    if (T == 0) return FORGE_OK;
+    cudaError_t e = forge::launch(moe_rank_kernel, dim3(E), dim3(256), 0, stream, 1, idx, rank, counts, T * top);
+    if (e != cudaSuccess) return forge::check_launch("moe_sort (rank)", e);
+    FORGE_DISPATCH_DTYPE(dtype, TT,
+        e = forge::launch(moe_gather_kernel<TT>, dim3(T * top), dim3(128), 0, stream, 1, (const TT*)x, idx, rank, counts, dest, (TT*)xg, W, top));
+    return forge::check_launch("moe_sort", e);
+}
+
+// ys fp32 [P, W] in sorted order; y fp32 [T, W].
+extern "C" int forge_moe_combine(const float* ys, const int32_t* dest, const float* wts, float* y, int T, int W, int top, cudaStream_t stream) {
+    if (T < 0 || W <= 0 || top <= 0) return forge::fail(FORGE_ERR_ARG, "moe_combine: bad sizes T=%d W=%d top=%d", T, W, top);
+    if (T == 0) return FORGE_OK;
+    cudaError_t e = forge::launch(moe_combine_kernel, dim3(T), dim3(128), 0, stream, 1, ys, dest, wts, y, W, top);
+    return forge::check_launch("moe_combine", e);
+}
+
+extern "C" const char* forge_last_error() { return forge::error_buffer(); }

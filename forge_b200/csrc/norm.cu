@@ -150,7 +150,49 @@ layernorm_kernel(const float* __restrict__ x, const float* __restrict__ w, const
     for (int c = threadIdx.x; c < H; c += kNormThreads) o[c] = forge::from_float<TOut>(fmaf((xr[c] - mean) * inv, w[c], b[c]));
 }
 
+// A sublayer's output y joins the stream through a norm of its own:  r <- r + mult * y / rms(y) * w_y, and, where the next
+// sublayer's input norm follows at once, out = r / rms(r) * w_next of the new r in the same pass (w_next null: r only).
+// One CTA per row; every sum runs over the row in the order of the fixed tree.
+template <typename TOut>
+__global__ void __launch_bounds__(kNormThreads)
+rmsnorm_add_kernel(const float* __restrict__ y, const float* __restrict__ w_y, float* __restrict__ r, const float* __restrict__ w_next,
+                   TOut* __restrict__ out, int H, float eps, float mult) {
+    __shared__ float red[32];
+    forge::pdl_launch_dependents();
+    forge::pdl_wait();
+    const float* yr = y + (size_t)blockIdx.x * H;
+    float* rr = r + (size_t)blockIdx.x * H;
+    float ss = 0.f;
+    for (int c = threadIdx.x; c < H; c += kNormThreads) ss = fmaf(yr[c], yr[c], ss);
+    ss = forge::block_sum(ss, red);
+    const float inv = 1.0f / sqrtf(ss / (float)H + eps);
+    float s2 = 0.f;
+    for (int c = threadIdx.x; c < H; c += kNormThreads) {
+        const float v = fmaf(mult, yr[c] * inv * w_y[c], rr[c]);
+        rr[c] = v;
+        s2 = fmaf(v, v, s2);
+    }
+    if (w_next == nullptr) return;
+    s2 = forge::block_sum(s2, red);
+    const float inv2 = 1.0f / sqrtf(s2 / (float)H + eps);
+    TOut* o = out + (size_t)blockIdx.x * H;
+    for (int c = threadIdx.x; c < H; c += kNormThreads) o[c] = forge::from_float<TOut>(rr[c] * inv2 * w_next[c]);
+}
+
 }  // namespace
+
+// y fp32 [R, H] (a sublayer's output), r fp32 [R, H] (the stream, updated in place), w_y fp32 [H]; w_next fp32 [H] and out
+// [R, H] of out_dtype, or both null.
+extern "C" int forge_rmsnorm_add(const float* y, const float* w_y, float* r, const float* w_next, void* out, int out_dtype, int R,
+                                 int H, float eps, float mult, cudaStream_t stream) {
+    if (R < 0 || H <= 0) return forge::fail(FORGE_ERR_ARG, "rmsnorm_add: bad sizes R=%d H=%d", R, H);
+    if ((w_next == nullptr) != (out == nullptr)) return forge::fail(FORGE_ERR_ARG, "rmsnorm_add: the next norm needs its weight and its output");
+    if (R == 0) return FORGE_OK;
+    cudaError_t e = cudaSuccess;
+    FORGE_DISPATCH_DTYPE(out_dtype, TO,
+        e = forge::launch(rmsnorm_add_kernel<TO>, dim3(R), dim3(kNormThreads), 0, stream, 1, y, w_y, r, w_next, (TO*)out, H, eps, mult));
+    return forge::check_launch("rmsnorm_add", e);
+}
 
 extern "C" int forge_layernorm(const float* x, const float* w, const float* b, void* out, int out_dtype, const int32_t* rows, int R,
                                int H, float eps, cudaStream_t stream) {

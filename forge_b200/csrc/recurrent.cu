@@ -10,8 +10,10 @@
 //                              a_t = sigmoid(y_t + a0)               (both terms read the state before the step)
 //   gated write (HGRN2):       S <- diag(f_t) S + (1 - f_t) v_t^T ;   o_t = S^T q_t          (no key: the forget gate also
 //                              f_t = l + (1 - l) sigmoid(x_t + b),  q_t = silu(y_t)            decides what is written)
+//   retention:                 S <- g S + k_t v_t^T ;   o_t = S^T q_t                         (one fixed decay g per head; q and k
+//                              rotated by their position, k times K^-1/2, by retention_prepare_kernel)
 //
-// In the third the state is [K, V] with V value channels that need not equal K; the first two have V = K.
+// In the last two the state is [K, V] with V value channels that need not equal K; the first two have V = K.
 //
 // A CTA per (request, head, 16 columns of S) walks the request's tokens of the step in order; column j of S (the K numbers
 // that meet value channel j) lives in the registers of eight neighbouring threads, so a token costs K/8 multiply-adds per
@@ -101,7 +103,7 @@ state_scan_kernel(ScanInput r, ScanInput k, ScanInput v, ScanInput d, ScanInput 
                   const int32_t* __restrict__ slots, float* __restrict__ out, const TA* __restrict__ last_in, int W,
                   long long prev_off, int N, int K, int KV, int vec) {
     constexpr int RPT = KMAX / kSplit;                                  // rows of S per thread
-    __shared__ __align__(16) float rs[2][kScanTokens][KMAX], ks[2][MODE == 2 ? 1 : kScanTokens][KMAX], ds[2][kScanTokens][KMAX];
+    __shared__ __align__(16) float rs[2][kScanTokens][KMAX], ks[2][MODE == 2 ? 1 : kScanTokens][KMAX], ds[2][MODE == 3 ? 1 : kScanTokens][KMAX];
     __shared__ __align__(16) float as[2][MODE == 1 ? kScanTokens : 1][KMAX], vs[2][kScanTokens][kCols], us[KMAX];
     __shared__ float is[2][kScanTokens];                                // MODE 1: 1 / (|k|^2 + 1e-6) of the staged tokens
     forge::pdl_launch_dependents();
@@ -113,7 +115,7 @@ state_scan_kernel(ScanInput r, ScanInput k, ScanInput v, ScanInput d, ScanInput 
     for (int i = tid; i < 2 * kScanTokens * KMAX; i += kScanThreads) {
         (&rs[0][0][0])[i] = 0.f;
         if (MODE != 2) (&ks[0][0][0])[i] = 0.f;          // (mode 2 has no keys: its ks is a stub that nothing reads)
-        (&ds[0][0][0])[i] = 0.f;
+        if (MODE != 3) (&ds[0][0][0])[i] = 0.f;          // (mode 3 has one decay per head: nothing staged)
         if (MODE == 1) (&as[0][0][0])[i] = 0.f;
     }
     for (int i = tid; i < 2 * kScanTokens * kCols; i += kScanThreads) (&vs[0][0][0])[i] = 0.f;
@@ -136,7 +138,7 @@ state_scan_kernel(ScanInput r, ScanInput k, ScanInput v, ScanInput d, ScanInput 
             const size_t t = (size_t)(tb + tt), c = (size_t)head * K + ch;
             stage_async(&rs[buf][tt][ch], r.p + t * r.ld + c, piece * 4);
             if (MODE != 2) stage_async(&ks[buf][tt][ch], k.p + t * k.ld + c, piece * 4);
-            stage_async(&ds[buf][tt][ch], d.p + t * d.ld + c, piece * 4);
+            if (MODE != 3) stage_async(&ds[buf][tt][ch], d.p + t * d.ld + c, piece * 4);
             if (MODE == 1) stage_async(&as[buf][tt][ch], a.p + t * a.ld + c, piece * 4);
         }
         const int tt = tid / kCols, jc = blockIdx.z * kCols + tid % kCols;              // values: this CTA's columns only
@@ -144,6 +146,7 @@ state_scan_kernel(ScanInput r, ScanInput k, ScanInput v, ScanInput d, ScanInput 
         if (MODE == 1 && tid < n) stage_async(&is[buf][tid], inv + (size_t)(tb + tid) * N + head, 4);
         asm volatile("cp.async.commit_group;" ::: "memory");
     };
+    const float head_decay = MODE == 3 ? d.p[head] : 0.f;       // mode 3: d is one number per head
     fetch(0, t_lo);
     int buf = 0;
     for (int tb = t_lo; tb < t_hi; tb += kScanTokens, buf ^= 1) {
@@ -176,6 +179,19 @@ state_scan_kernel(ScanInput r, ScanInput k, ScanInput v, ScanInput d, ScanInput 
                         if (e & 1) acc1 = fmaf(rv[e], fmaf(uv[e], kv, S[ii]), acc1);
                         else acc0 = fmaf(rv[e], fmaf(uv[e], kv, S[ii]), acc0);
                         S[ii] = fmaf(dv[e], S[ii], kv);
+                    }
+                }
+            } else if (MODE == 3) {
+#pragma unroll
+                for (int c4 = 0; c4 < RPT / 4; ++c4) {
+                    const float4 rr = r4[c4 * kSplit], kk = k4[c4 * kSplit];
+                    const float rv[4] = {rr.x, rr.y, rr.z, rr.w}, kv4[4] = {kk.x, kk.y, kk.z, kk.w};
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        const int ii = c4 * 4 + e;
+                        S[ii] = fmaf(head_decay, S[ii], kv4[e] * vj);
+                        if (e & 1) acc1 = fmaf(rv[e], S[ii], acc1);
+                        else acc0 = fmaf(rv[e], S[ii], acc0);
                     }
                 }
             } else if (MODE == 2) {
@@ -300,6 +316,31 @@ __global__ void tanh_rows_kernel(ScanInput in, TA* __restrict__ out, int T, int 
     out[i] = forge::from_float<TA>(tanhf(in.p[(i / n) * in.ld + i % n]));
 }
 
+// Retention's q and k on their way into the recurrence, in place, a warp per (token, head): the first rot_dims channels of
+// both turn by position * freq (channel i paired with i + rot_dims/2), then k is multiplied by k_scale.
+__global__ void __launch_bounds__(128)
+retention_prepare_kernel(float* __restrict__ q, int ld_q, float* __restrict__ k, int ld_k, const int32_t* __restrict__ positions,
+                         const float* __restrict__ freq, int rot_dims, float k_scale, int T, int N, int K) {
+    forge::pdl_wait();             // (no early word: the scan follows, see scan_gates_kernel)
+    const int w = blockIdx.x * 4 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+    if (w >= T * N) return;
+    const size_t t = w / N;
+    const int head = w % N, half = rot_dims >> 1;
+    const float pos = (float)positions[t];
+    float* qh = q + t * ld_q + head * K;
+    float* kh = k + t * ld_k + head * K;
+    for (int i = lane; i < half; i += 32) {
+        float sn, cs;
+        sincosf(pos * freq[i], &sn, &cs);
+        const float qu = qh[i], qv = qh[i + half], ku = kh[i], kv = kh[i + half];
+        qh[i] = qu * cs - qv * sn;
+        qh[i + half] = qv * cs + qu * sn;
+        kh[i] = (ku * cs - kv * sn) * k_scale;
+        kh[i + half] = (kv * cs + ku * sn) * k_scale;
+    }
+    for (int c = rot_dims + lane; c < K; c += 32) kh[c] *= k_scale;
+}
+
 template <int MODE, typename TA>
 cudaError_t launch_scan(int kmax, dim3 grid, cudaStream_t stream, ScanInput r, ScanInput k, ScanInput v, ScanInput d, ScanInput a,
                         const float* bonus, const float* inv, float* state, long long stride, const int32_t* q_start, const int32_t* slots,
@@ -308,7 +349,7 @@ cudaError_t launch_scan(int kmax, dim3 grid, cudaStream_t stream, ScanInput r, S
     case KM:                                                                                                                 \
         return forge::launch(state_scan_kernel<KM, MODE, TA>, grid, dim3(kScanThreads), 0, stream, 1, r, k, v, d, a, bonus, inv, state, \
                              stride, q_start, slots, out, last_in, W, prev_off, N, K, KV, vec);
-    if constexpr (MODE == 2) {            // the gated write stages no keys: heads of up to 256 key channels fit its shared memory
+    if constexpr (MODE == 2 || MODE == 3) {   // the gated write stages no keys, retention no decays: heads of up to 256 key channels fit
         switch (kmax) {
             FORGE_SCAN_CASE(192) FORGE_SCAN_CASE(256)
             default: break;
@@ -375,6 +416,33 @@ extern "C" int forge_state_scan(int mode, const float* r, int ld_r, const float*
                                           (const __nv_bfloat16*)last_in, W, prev_off, N, K, K, vec);
     }
     return forge::check_launch("state_scan", e);
+}
+
+// Retention over the step's tokens: q, k fp32 (row t at p + t * ld, head n's K channels at columns n*K ..) are rotated and
+// scaled IN PLACE, then S <- decay[n] S + k v^T, out = S^T q per head; v and out have N*KV columns, a head's state is [K, KV].
+// freq fp32 [rot_dims / 2] (null with rot_dims 0); decay fp32 [N].
+extern "C" int forge_retention_scan(float* q, int ld_q, float* k, int ld_k, const float* v, int ld_v, const int32_t* positions,
+                                    const float* freq, int rot_dims, float k_scale, const float* decay, float* state,
+                                    long long state_stride, const int32_t* q_start, const int32_t* slots, float* out, int T, int S,
+                                    int N, int K, int KV, cudaStream_t stream) {
+    if (T < 0 || S < 0 || N <= 0 || K <= 0 || KV <= 0 || rot_dims < 0 || rot_dims > K || (rot_dims & 1))
+        return forge::fail(FORGE_ERR_ARG, "retention_scan: bad sizes S=%d N=%d K=%d V=%d rot=%d", S, N, K, KV, rot_dims);
+    if (K > 256) return forge::fail(FORGE_ERR_UNSUPPORTED, "retention_scan: heads of %d key channels (at most 256)", K);
+    if (state_stride < (long long)N * K * KV) return forge::fail(FORGE_ERR_ARG, "retention_scan: state rows are too short");
+    if (rot_dims > 0 && !freq) return forge::fail(FORGE_ERR_ARG, "retention_scan: a rotation needs its frequencies");
+    if (S == 0 || T == 0) return FORGE_OK;
+    const unsigned blocks = (unsigned)(((size_t)T * N + 3) / 4);
+    cudaError_t e = forge::launch(retention_prepare_kernel, dim3(blocks), dim3(128), 0, stream, 1, q, ld_q, k, ld_k, positions, freq, rot_dims,
+                                  k_scale, T, N, K);
+    if (e != cudaSuccess) return forge::check_launch("retention_scan (prepare)", e);
+    const int kmax = K <= 128 ? (K + 31) / 32 * 32 : (K <= 192 ? 192 : 256);
+    const dim3 grid(S, N, (KV + kCols - 1) / kCols);
+    ScanInput Q{q, ld_q}, Kk{k, ld_k}, V{v, ld_v}, D{decay, 0};
+    auto aligned = [](const float* p, int ld) { return ((uintptr_t)p & 15) == 0 && ld % 4 == 0; };
+    const int vec = (K % 4 == 0 && aligned(q, ld_q) && aligned(k, ld_k)) ? 1 : 0;
+    e = launch_scan<3, float>(kmax, grid, stream, Q, Kk, V, D, D, nullptr, nullptr, state, state_stride, q_start, slots, out, nullptr, 0, 0,
+                              N, K, KV, vec);
+    return forge::check_launch("retention_scan", e);
 }
 
 // h, out of type dtype: [T, W] and [n_mix, T, W]; mu fp32 [n_mix, W]; the kept row of request s: state + slots[s] * stride + prev_off.

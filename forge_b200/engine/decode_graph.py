@@ -91,7 +91,7 @@ class DecodeGraph:
         self.ring_events[i] = ev
 
     def _forward(self):
-        logits = self.runner.model.forward(self.batch, self.runner.storage.layers)
+        logits = self.runner.model.forward(self.batch, self.runner.storage.layers, embedding_cache=self.runner.storage.embedding)
         return logits, kernels.argmax(logits)
 
     def run(self, hs, tokens_from=None):

@@ -33,6 +33,8 @@ class Model:
         for i, spec in enumerate(plan.layers):
             if spec.cache_from is not None and not 0 <= spec.cache_from < n:
                 raise ConfigError(f"layer {i}: cache_from {spec.cache_from} is not a layer")
+        if getattr(self.embedding, "needs_batch", False) and plan.add_embedding_before:
+            raise ConfigError("an embedding that keeps state cannot be added to the stream again within a step")
         self.loaded = False
         self._fused = None
         self._replay_ok, self._replay_from, self._replay_tensors = False, 0, []
@@ -91,6 +93,11 @@ class Model:
     def cache_specs(self):
         """Per schedule position: what that run of its layer's mixer keeps."""
         return [self.blocks[i].mixer.cache_spec() for i in self.plan.schedule]
+
+    def embedding_cache_spec(self):
+        """What the embedding keeps per request (a design whose embedding looks at the token before), or None."""
+        spec = getattr(self.embedding, "cache_spec", None)
+        return spec() if spec is not None else None
 
     def cache_from(self):
         """Per schedule position: the earlier position whose cache it reads instead of keeping one (None:
@@ -161,11 +168,15 @@ class Model:
         return True
 
     # ---------------------------------------------------------------------------------- forward
-    def forward(self, batch, position_caches, workspace=None):
-        """Runs the step's tokens through the schedule; ``position_caches[p]`` is the cache of the p-th run.
+    def forward(self, batch, position_caches, workspace=None, embedding_cache=None):
+        """Runs the step's tokens through the schedule; ``position_caches[p]`` is the cache of the p-th run,
+        ``embedding_cache`` what the embedding keeps (``embedding_cache_spec``).
         Returns fp32 logits [R,V] at ``batch.logits_rows`` (None if no row is wanted).  ``workspace``: the open
         StepWorkspace that the kernels' outputs are cut from; a layer's share of it is given back after the layer."""
-        residual = self.embedding.forward(batch.token_ids, status=batch.status)
+        if getattr(self.embedding, "needs_batch", False):
+            residual = self.embedding.forward_step(batch, embedding_cache)
+        else:
+            residual = self.embedding.forward(batch.token_ids, status=batch.status)
         if self._fused_decode_applies(batch):
             fused, group = self._fused
             g = batch.groups[group]

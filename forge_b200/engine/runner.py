@@ -84,7 +84,7 @@ class ModelRunner:
             cache_tokens = cap if per_page == 0 else min(cap, int(free * memory_fraction) // per_page * self.page_size)
         self.num_pages = max(1, -(-int(cache_tokens) // self.page_size))
         self.storage = CacheStorage(specs, cfrom, self.page_size, self.num_pages, self.max_requests, self.dtype,
-                                    self.device)
+                                    self.device, embedding_spec=self.model.embedding_cache_spec())
         self.manager = self.storage.manager
         # width of a request's block table.  A group that keeps every key can never give a request more
         # pages than its pool has; a windowed group hands old pages back but its table keeps its logical
@@ -181,7 +181,7 @@ class ModelRunner:
         with self.workspace.step() as ws:
             batch = build_step_batch(entries, self.manager, self.device, self.max_pages_per_request, status=self.status)
             self.storage.zero_state_slots(self.manager.take_fresh_slots())
-            logits = self.model.forward(batch, self.storage.layers, workspace=ws)
+            logits = self.model.forward(batch, self.storage.layers, workspace=ws, embedding_cache=self.storage.embedding)
         for e in entries:
             self.manager.release_out_of_window(e.req_id)
         return logits

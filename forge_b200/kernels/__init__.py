@@ -33,6 +33,8 @@ _P, _I, _F, _LL = c_void_p, c_int, c_float, ctypes.c_longlong
 _SIGNATURES = {
     "core": {
         "forge_embedding": [_P, _P, _I, _P, _I, _I, _I, _F, _I, _P, _P],
+        "forge_embedding_pair": [_P, _P, _P, _P, _P, _P, _LL, _P, _P, _I, _P, _I, _I, _I, _I, _LL, _LL, _P, _P],
+        "forge_rmsnorm_add": [_P, _P, _P, _P, _P, _I, _I, _I, _F, _F, _P],
         "forge_layernorm": [_P, _P, _P, _P, _I, _P, _I, _I, _F, _P],
         "forge_act_rows": [_P, _I, _P, _I, _I, _I, _I, _P],
         "forge_rmsnorm": [_P, _P, _P, _I, _P, _I, _I, _F, _P],
@@ -74,6 +76,19 @@ _SIGNATURES = {
         "forge_token_shift": [_P, _P, _LL, _LL, _P, _P, _P, _P, _P, _I, _I, _I, _I, _P],
         "forge_head_finish": [_P, _P, _P, _I, _P, _I, _I, _I, _I, _F, _I, _F, _I, _LL, _P],
         "forge_tanh_rows": [_P, _I, _P, _I, _I, _I, _P],
+        "forge_retention_scan": [_P, _I, _P, _I, _P, _I, _P, _P, _I, _F, _P, _P, _LL, _P, _P, _P, _I, _I, _I, _I, _I, _P],
+    },
+    "latent": {
+        "forge_latent_prepare": [_P, _I, _P, _P, _P, _F, _P, _P, _P, _P, _I, _I, _I, _I, _I, _F, _P],
+        "forge_head_linear": [_P, _I, _LL, _I, _P, _P, _I, _LL, _I, _P, _P, _F, _I, _I, _I, _I, _I, _P],
+        "forge_latent_attention": [_P] * 8 + [_I] * 8 + [_F, _I, _I, _P],
+    },
+    "moe": {
+        "forge_moe_route": [_P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _P],
+        "forge_moe_pair_gate_up": [_P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _LL, _P],
+        "forge_moe_pair_down": [_P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _P],
+        "forge_moe_sort": [_P, _I, _P, _P, _P, _P, _P, _I, _I, _I, _I, _P],
+        "forge_moe_combine": [_P, _P, _P, _P, _I, _I, _I, _P],
     },
     "decode_layers": {
         "forge_decode_layers_desc_bytes": [],
@@ -92,6 +107,7 @@ _libs = {}
 _CHECK_ENTRIES = {"core": ["forge_checks_configure_rope", "forge_checks_configure_attention_simt"],
                   "mixers": ["forge_checks_configure_attention_headmix", "forge_checks_configure_attention_headmix_mma",
                              "forge_checks_configure_attention_scored", "forge_checks_configure_attention_scored_mma"],
+                  "latent": ["forge_checks_configure_attention_latent"],
                   "gemm_sm100": ["forge_checks_configure_gemm_sm100"],
                   "attention_mma": ["forge_checks_configure_attention_mma", "forge_checks_configure_attention_decode_stream"],
                   "attention_sm100": ["forge_checks_configure_attention_sm100"]}
@@ -521,6 +537,39 @@ def embedding(ids, table, out=None, status=None, scale=1.0, add=False):
     _check(lib, lib.forge_embedding(_need(ids, "ids", torch.int32), _need(table, "table", ndim=2),
                                     dtype_code(table.dtype), _need(out, "out", torch.float32), T, H, V, float(scale),
                                     1 if add else 0, _opt(status, "status", torch.int32), _stream()), "embedding")
+    return out
+
+
+def embedding_pair(batch, table, pair_table, last, buckets, mul_prev, mul_cur, status=None):
+    """out[t,:] = table[id_t,:] + pair_table[row_t,:] as float32 [T,H], row_t = (id_{t-1} * mul_prev + id_t * mul_cur) mod buckets,
+    or ``buckets`` (the table's last row) at position 0.  The token before a portion's first token is the one kept per request
+    slot in ``last`` (int32 [slots, n]), which the kernel replaces with the last token the step brings for the request."""
+    lib = library("core")
+    ids = batch.token_ids
+    T, (V, H) = ids.numel(), table.shape
+    if tuple(pair_table.shape) != (buckets + 1, H) or pair_table.dtype != table.dtype:
+        raise KernelError(f"embedding_pair: the second table is {tuple(pair_table.shape)} {pair_table.dtype}, expected {(buckets + 1, H)} {table.dtype}")
+    out = new_tensor((T, H), torch.float32, table.device)
+    _check(lib, lib.forge_embedding_pair(
+        _need(ids, "ids", torch.int32), _need(batch.positions, "positions", torch.int32), _need(batch.tok_req, "tok_req", torch.int32),
+        _need(batch.q_start, "q_start", torch.int32), _need(batch.slots, "slots", torch.int32), _need(last, "last", torch.int32, 2),
+        last.shape[1], _need(table, "table", ndim=2), _need(pair_table, "pair_table", ndim=2), dtype_code(table.dtype),
+        _need(out, "out", torch.float32), T, H, V, int(buckets), int(mul_prev), int(mul_cur), _opt(status, "status", torch.int32),
+        _stream()), "embedding_pair")
+    return out
+
+
+def rmsnorm_add(y, w_y, residual, eps, mult=1.0, w_next=None, out_dtype=None):
+    """residual += mult * y / rms(y) * w_y over the rows of float32 y, residual [T,H]; with ``w_next`` also returns
+    residual / rms(residual) * w_next of the new rows in ``out_dtype`` (the next sublayer's input), else None."""
+    lib = library("core")
+    T, H = y.shape
+    if tuple(residual.shape) != (T, H) or w_y.numel() != H or (w_next is not None and w_next.numel() != H):
+        raise KernelError(f"rmsnorm_add: y {tuple(y.shape)}, residual {tuple(residual.shape)}, weights of {w_y.numel()}")
+    out = new_tensor((T, H), out_dtype, y.device) if w_next is not None else None
+    _check(lib, lib.forge_rmsnorm_add(_need(y, "y", torch.float32, 2), _need(w_y, "w_y", torch.float32), _need(residual, "residual", torch.float32, 2),
+                                      _opt(w_next, "w_next", torch.float32), _opt(out, "out", out_dtype),
+                                      dtype_code(out_dtype) if out is not None else F32, T, H, float(eps), float(mult), _stream()), "rmsnorm_add")
     return out
 
 
@@ -965,6 +1014,161 @@ def state_scan(kind, r, k, v, x, w0, state, batch, N, K, y=None, a0=None, bonus=
         _stream()), "state_scan")
     count_launches(1)              # the kernel that makes the decays (and removal rates) from x (and y), in place
     return out
+
+
+def retention_scan(q, k, v, batch, freq, k_scale, decay, state, N, K, KV):
+    """Retention over the step's tokens, request by request, from and into ``state`` fp32 [slots, N*K*KV]: q, k ((fp32 matrix,
+    first column) pairs, N*K columns) are rotated IN PLACE on their first 2*len(freq) channels (channel i with i + half) by
+    position * freq, k is multiplied by ``k_scale``; S <- decay[n] S + k v^T, out = S^T q per head.  v (N*KV columns); returns
+    fp32 [T, N*KV]."""
+    lib = library("mixers")
+    T = q[0].shape[0]
+    out = new_tensor((T, N * KV), torch.float32, q[0].device)
+    (qp, ql), (kp, kl), (vp, vl) = _cols(*q), _cols(*k), _cols(*v)
+    rot = 0 if freq is None else 2 * freq.numel()
+    _check(lib, lib.forge_retention_scan(
+        qp, ql, kp, kl, vp, vl, _need(batch.positions, "positions", torch.int32), _opt(freq, "freq", torch.float32) if rot else None, rot,
+        float(k_scale), _need(decay, "decay", torch.float32), _need(state, "state", torch.float32, 2), state.shape[1],
+        _need(batch.q_start, "q_start", torch.int32), _need(batch.slots, "slots", torch.int32), _need(out, "out", torch.float32), T,
+        batch.num_requests, N, K, KV, _stream()), "retention_scan")
+    count_launches(1)              # the kernel that rotates and scales q and k, in place
+    return out
+
+
+# ---------------------------------------------------------------------------------------------- latent attention
+
+LATENT_KEYS_PER_CHUNK = 32          # fixed: a token's sums must not depend on the step's shape
+
+
+def latent_prepare(proj, batch, slot_mapping, cache, freq, amp, wq, wc, Cq, C, R, eps, act_dtype):
+    """proj fp32 [T, Cq (+ C + R)]: the query latent normed (weight ``wq``) -> [T, Cq] in ``act_dtype``; with C > 0 the normed
+    key/value latent (weight ``wc``) and the rotated shared key part go to ``slot_mapping`` in ``cache`` (rows of C + R)."""
+    lib = library("latent")
+    T, ld = proj.shape
+    cq = new_tensor((T, Cq), act_dtype, proj.device)
+    store = C > 0 and cache is not None and slot_mapping is not None
+    if store and cache.dtype != act_dtype:
+        raise KernelError("latent_prepare: cache and activation dtypes differ")
+    _check(lib, lib.forge_latent_prepare(
+        _need(proj, "proj", torch.float32, 2), ld, _need(batch.positions, "positions", torch.int32),
+        _need(slot_mapping, "slot_mapping", torch.int32) if store else None, _opt(freq, "freq", torch.float32), float(amp),
+        _need(wq, "wq", torch.float32), _opt(wc, "wc", torch.float32), _need(cq, "cq", act_dtype), _need(cache, "cache") if store else None,
+        dtype_code(act_dtype), T, Cq, C if ld > Cq else 0, R, float(eps), _stream()), "latent_prepare")
+    return cq
+
+
+def head_linear(x, w, H, K, N, out_dtype, R=0, positions=None, freq=None, amp=1.0):
+    """out[t, h, :N] = sum_k x[t, h, k] w[h, k, :] for the H heads of x [T, H*(K+R)] (fp32 or the weights' type); with R > 0 a head's
+    last R channels are rotated by position * freq (channel 2i with 2i+1, cos and sin times ``amp``) and follow the N outputs.
+    w [H, K, N] in ``out_dtype``; returns [T, H*(N+R)] in ``out_dtype``."""
+    lib = library("latent")
+    T = x.shape[0]
+    if x.shape[1] != H * (K + R) or tuple(w.shape) != (H, K, N) or w.dtype != out_dtype:
+        raise KernelError(f"head_linear: x {tuple(x.shape)}, w {tuple(w.shape)} {w.dtype} do not fit {H} heads of {K}+{R} -> {N}")
+    out = new_tensor((T, H * (N + R)), out_dtype, x.device)
+    _check(lib, lib.forge_head_linear(
+        _need(x, "x", ndim=2), dtype_code(x.dtype), H * (K + R), K + R, _need(w, "w"), _need(out, "out", out_dtype), dtype_code(out_dtype),
+        H * (N + R), N + R, _opt(positions, "positions", torch.int32), _opt(freq, "freq", torch.float32), float(amp), T, H, K, N, R,
+        _stream()), "head_linear")
+    return out
+
+
+def latent_tile_shape(H, C, R, single_tokens=False):
+    """(tokens per tile, heads per CTA) of the latent attention for these sizes: of the shapes that fit a CTA's shared memory
+    the one with the most rows, among equals the one with more heads (so that a chunk's rows are loaded for as many heads
+    as possible)."""
+    KT = LATENT_KEYS_PER_CHUNK
+    best = None
+    for TQ in ((1,) if single_tokens else (16, 8, 4, 2, 1)):
+        for HG in sorted({H, -(-H // 2), -(-H // 4), -(-H // 8), -(-H // 16), 1}, reverse=True):
+            if 4 * (TQ * HG * (2 * C + R + KT + 3) + KT * (C + R + 1)) <= HEADMIX_SMEM_LIMIT:
+                if best is None or TQ * HG > best[0] * best[1]:
+                    best = (TQ, HG)
+                break
+    if best is None:
+        raise KernelError(f"latent attention: a latent of {C}+{R} channels does not fit a CTA's shared memory")
+    return best
+
+
+def latent_attention(q, cache, group_batch, batch, H, C, R, page_size, scale):
+    """Causal softmax attention of every token's H absorbed queries (q [T, H*(C+R)]) over its request's latent rows in
+    ``cache`` (rows of C + R; the values are a row's first C channels); returns the weighted latents [T, H*C] in q's type."""
+    lib = library("latent")
+    T = q.shape[0]
+    if cache.dtype != q.dtype:
+        raise KernelError("latent_attention: q and cache dtypes differ")
+    single = getattr(batch, "decode_only", False) or batch.num_tokens == batch.num_requests
+    TQ, HG = latent_tile_shape(H, C, R, single_tokens=single)
+    t0, tn, tiles = headmix_plan(batch, TQ, q.device)
+    out = new_tensor((T, H * C), q.dtype, q.device)
+    _check(lib, lib.forge_latent_attention(
+        _need(q, "q", ndim=2), _need(cache, "cache"), _need(group_batch.block_table, "block_table", torch.int32, 2),
+        _need(batch.tok_req, "tok_req", torch.int32), _need(batch.positions, "positions", torch.int32), _opt(t0, "tile_t0", torch.int32),
+        _opt(tn, "tile_n", torch.int32), _need(out, "out", q.dtype), dtype_code(q.dtype), tiles, H, HG, C, R, page_size,
+        group_batch.block_table.shape[1], float(scale), TQ, LATENT_KEYS_PER_CHUNK, _stream()), "latent_attention")
+    return out
+
+
+# ---------------------------------------------------------------------------------------------- routed experts
+
+def moe_route(x, router, top, softmax=False, renorm=False):
+    """(int32 [T, top] experts, fp32 [T, top] weights): the ``top`` largest of sigmoid (or softmax) of router . x per token, the lower
+    index winning a tie; the weights are those scores, divided by their sum with ``renorm``.  router fp32 [E, W]; fp32 arithmetic."""
+    lib = library("moe")
+    T, W = x.shape
+    E = router.shape[0]
+    idx = new_tensor((T, top), torch.int32, x.device)
+    wts = new_tensor((T, top), torch.float32, x.device)
+    _check(lib, lib.forge_moe_route(_need(x, "x", ndim=2), dtype_code(x.dtype), _need(router, "router", torch.float32, 2), _need(idx, "idx"),
+                                    _need(wts, "wts"), T, W, E, int(top), 1 if softmax else 0, 1 if renorm else 0, _stream()), "moe_route")
+    return idx, wts
+
+
+def moe_pairs(x, idx, wts, w_gate_up, w_down):
+    """y fp32 [T, W] = sum_k wts[t,k] * W_down[e] (silu(W_gate[e] x_t) * (W_up[e] x_t)), e = idx[t,k], every (token, expert) pair
+    on its own; w_gate_up [E, 2F, W] (row 2j the gate's, 2j+1 the up's), w_down [E, W, F] in x's type.  Reads everything from
+    device memory."""
+    lib = library("moe")
+    T, W = x.shape
+    E, F2, _ = w_gate_up.shape
+    F = F2 // 2
+    top = idx.shape[1]
+    act = new_tensor((T * top, F), x.dtype, x.device)
+    gp = _need(w_gate_up, "w_gate_up", x.dtype)
+    _check(lib, lib.forge_moe_pair_gate_up(_need(x, "x", ndim=2), gp, gp + W * x.element_size(), _need(idx, "idx", torch.int32),
+                                           _need(act, "act"), dtype_code(x.dtype), T, W, F, top, 2 * W, _stream()), "moe_pair_gate_up")
+    y = new_tensor((T, W), torch.float32, x.device)
+    _check(lib, lib.forge_moe_pair_down(_need(act, "act"), _need(w_down, "w_down", x.dtype), _need(idx, "idx", torch.int32),
+                                        _need(wts, "wts", torch.float32), _need(y, "y"), dtype_code(x.dtype), T, W, F, top, _stream()),
+           "moe_pair_down")
+    return y
+
+
+def moe_sort(x, idx, E):
+    """The (token, expert) pairs ranked by (expert, token): returns (xg [T*top, W]: each pair's input row at its rank, counts int32 [E],
+    dest int32 [T, top]: the rank of every pair)."""
+    lib = library("moe")
+    T, W = x.shape
+    top = idx.shape[1]
+    rank = new_tensor((T * top,), torch.int32, x.device)
+    dest = new_tensor((T, top), torch.int32, x.device)
+    counts = new_tensor((E,), torch.int32, x.device)
+    xg = new_tensor((T * top, W), x.dtype, x.device)
+    _check(lib, lib.forge_moe_sort(_need(x, "x", ndim=2), dtype_code(x.dtype), _need(idx, "idx", torch.int32), _need(rank, "rank"),
+                                   _need(counts, "counts"), _need(dest, "dest"), _need(xg, "xg"), T, W, E, top, _stream()), "moe_sort")
+    count_launches(1)
+    return xg, counts, dest
+
+
+def moe_combine(ys, dest, wts):
+    """y fp32 [T, W] = sum_k wts[t,k] * ys[dest[t,k], :], k in order."""
+    lib = library("moe")
+    T, top = dest.shape
+    W = ys.shape[1]
+    y = new_tensor((T, W), torch.float32, ys.device)
+    _check(lib, lib.forge_moe_combine(_need(ys, "ys", torch.float32, 2), _need(dest, "dest", torch.int32), _need(wts, "wts", torch.float32),
+                                      _need(y, "y"), T, W, top, _stream()), "moe_combine")
+    return y
 
 
 def token_shift(h, state, prev_off, batch, mu):

@@ -1,7 +1,7 @@
 from .base import (CATEGORIES, CompositeCacheSpec, KVCacheSpec, Part, Runtime, StateSpec, build_part, register_part, registered_parts,
                    unregister_part)
-from . import (attention, block, embedding, feedforward, headmix_attention, norm, position,  # noqa: F401  (register the
-               recurrent, scored_attention, side_by_side)                                    # built-in parts)
+from . import (attention, block, embedding, feedforward, headmix_attention, latent_attention, norm, position,  # noqa: F401  (register
+               recurrent, routed, scored_attention, side_by_side)                                            # the built-in parts)
 from .block import build_block
 from .linear import Linear
 

@@ -44,7 +44,7 @@ class KVCacheSpec:
     ``window``: only the last ``window`` positions are ever read (None: all of them), and, with ``keep_first``, the first
     ``keep_first`` positions of the sequence, which are never given back.  ``v_head_dim``: size of a value head when
     it is not the key's; a page is then one row, [num_kv_heads, page_size, head_dim] keys followed by [num_kv_heads,
-    page_size, v_head_dim] values."""
+    page_size, v_head_dim] values; 0: no values are kept (the mixer reads them out of the key rows)."""
     num_kv_heads: int
     head_dim: int
     window: Optional[int] = None

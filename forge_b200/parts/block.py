@@ -4,6 +4,9 @@
 (reference: src/inference/engines/generic_engine.cpp:931-938, 1045-1052, 1080).
 "parallel":  r += mixer(norm_a(r)) + feed_forward(norm_b(r)), both branches of the same r.  The additions happen in
 the epilogue of each part's last matrix product, in fp32.
+"sandwich":  r += m * norm_b(mixer(norm_a(r)));  r += m * norm_d(feed_forward(norm_c(r))): every sublayer's OUTPUT goes
+through an RMS norm of its own before it joins the stream, times a number m.  The output norm, the addition and the next
+sublayer's input norm are one kernel.
 """
 from ..weights.loader import TensorSpec  # noqa: F401  (re-exported for part authors)
 from .base import Part, build_part, register_part
@@ -131,6 +134,56 @@ class ParallelBlock(Part):
             self.feed_forward.forward(x_ff, residual)
 
 
+class SandwichBlock(Part):
+    """``norms``: {"mixer_in", "mixer_out", "ff_in", "ff_out"} (the last two None in a layer without feed-forward), all RMS norms
+    with one eps; ``layer_spec.block_params``: {"residual_mult": m}.  Mixer and feed-forward are called without a stream to add
+    into and return their output."""
+    graph_safe = True
+
+    def sub_parts(self):
+        return [p for p in (self.mixer, self.feed_forward, *self.norms.values()) if p is not None]
+
+    def __init__(self, rt, layer_spec):
+        from ..config.base import ConfigError
+        from .norm import RMSNorm
+        self.rt = rt
+        self.mult = float((layer_spec.block_params or {}).get("residual_mult", 1.0))
+        self.mixer = build_part("mixer", layer_spec.mixer, rt)
+        self.feed_forward = build_part("feed_forward", layer_spec.feed_forward, rt)
+        self.norms = {k: None if layer_spec.norms.get(k) is None else build_part("norm", layer_spec.norms[k], rt)
+                      for k in ("mixer_in", "mixer_out", "ff_in", "ff_out")}
+        present = [n for n in self.norms.values() if n is not None]
+        if self.norms["mixer_in"] is None or self.norms["mixer_out"] is None or (self.norms["ff_in"] is None) != (self.norms["ff_out"] is None):
+            raise ConfigError("a sandwich layer needs a norm before and after its mixer, and both or none around its feed-forward")
+        if any(not isinstance(n, RMSNorm) or n.eps != present[0].eps for n in present):
+            raise ConfigError("a sandwich layer's norms are RMS norms with one eps")
+
+    def _children(self):
+        return [p for p in (self.mixer, self.feed_forward, *self.norms.values()) if p is not None]
+
+    def tensor_specs(self):
+        specs = {}
+        for part in self._children():
+            specs.update(part.tensor_specs())
+        return specs
+
+    def bind(self, tensors):
+        for part in self._children():
+            part.bind({name: tensors[name] for name in part.tensor_specs() if name in tensors})
+
+    def forward(self, residual, batch, cache):
+        from .. import kernels
+        n = self.norms
+        y = self.mixer.forward(n["mixer_in"].forward(residual), batch, cache, None)
+        if n["ff_in"] is None:
+            kernels.rmsnorm_add(y, n["mixer_out"].weight, residual, n["mixer_out"].eps, self.mult)
+            return
+        x = kernels.rmsnorm_add(y, n["mixer_out"].weight, residual, n["mixer_out"].eps, self.mult, w_next=n["ff_in"].weight,
+                                out_dtype=self.rt.dtype)
+        y = self.feed_forward.forward(x, None)
+        kernels.rmsnorm_add(y, n["ff_out"].weight, residual, n["ff_out"].eps, self.mult)
+
+
 def build_block(layer_spec, rt):
     from .base import _REGISTRY
     from ..config.base import ConfigError
@@ -143,3 +196,4 @@ def build_block(layer_spec, rt):
 
 register_part("block", "pre_norm", PreNormBlock, replace=True)
 register_part("block", "parallel", ParallelBlock, replace=True)
+register_part("block", "sandwich", SandwichBlock, replace=True)

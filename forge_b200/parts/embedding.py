@@ -32,6 +32,43 @@ class TokenEmbedding(Part):
         return kernels.embedding(token_ids, self.table, out=add_into, status=status, scale=self.scale, add=add_into is not None)
 
 
+class PairEmbedding(TokenEmbedding):
+    """The token's row plus a row of a second table that the token and the one before it choose together:
+    row (previous * mul_prev + token * mul_cur) mod buckets, or the row after the hashed ones for a sequence's first token.
+    The last token of a request's portion is state: one int32 per request slot (``cache_spec``), so that the next portion,
+    or the next single token, finds its predecessor whatever the cut.  ``forward_step`` takes the step's batch."""
+    needs_batch = True
+
+    def __init__(self, rt, vocab_size, hidden_size, buckets, mul_prev, mul_cur, names=None):
+        super().__init__(rt, vocab_size, hidden_size, names={"weight": "embed", "pair": "bigram", **(names or {})})
+        if buckets <= 0:
+            from ..config.base import ConfigError
+            raise ConfigError(f"the second embedding table needs a positive number of hashed rows, not {buckets}")
+        self.buckets, self.mul_prev, self.mul_cur = int(buckets), int(mul_prev), int(mul_cur)
+        self.pair_table = None
+
+    def tensor_specs(self):
+        specs = super().tensor_specs()
+        specs[self.names["pair"]] = TensorSpec((self.buckets + 1, self.hidden_size), role="embedding")
+        return specs
+
+    def bind(self, tensors):
+        super().bind(tensors)
+        self.pair_table = self._matrix(tensors[self.names["pair"]])
+
+    def cache_spec(self):
+        import torch
+        from .base import StateSpec
+        return StateSpec((1,), torch.int32)
+
+    def forward(self, token_ids, status=None, add_into=None):
+        raise RuntimeError("this embedding looks at the token before: it runs on a step's batch (forward_step)")
+
+    def forward_step(self, batch, cache):
+        return kernels.embedding_pair(batch, self.table, self.pair_table, cache.state, self.buckets, self.mul_prev, self.mul_cur,
+                                      status=batch.status)
+
+
 class LMHead(Part):
     graph_safe = True
     def __init__(self, rt, vocab_size, hidden_size, tied=False, names=None):
@@ -56,4 +93,5 @@ class LMHead(Part):
 
 
 register_part("embedding", "embedding", TokenEmbedding, replace=True)
+register_part("embedding", "pair_embedding", PairEmbedding, replace=True)
 register_part("lm_head", "lm_head", LMHead, replace=True)

@@ -41,8 +41,9 @@ class SwiGLU(Part):
         return (self.activation, self.gate_up.replay_key(), self.down.replay_key())
 
     def forward(self, x, residual):
+        """Adds the output into ``residual``, or (``residual`` None) returns it as a new fp32 [T, H]."""
         act = self.gate_up.forward(x, epilogue=self.activation)    # [T,I] in the activation type
-        self.down.forward(act, accumulate_into=residual)
+        return self.down.forward(act, accumulate_into=residual)
 
 
 class GeGLU(SwiGLU):

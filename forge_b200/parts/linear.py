@@ -23,13 +23,14 @@ class Linear:
     def replay_key(self):
         return ("linear", tuple(self.weight.shape), self.weight.dtype, self.bias is None, self.tensor_core)
 
-    def forward(self, x, accumulate_into=None, epilogue="none"):
+    def forward(self, x, accumulate_into=None, epilogue="none", out=None):
         """x [M,K] in rt.dtype.
         epilogue "none":   fp32 [M,N] (added into ``accumulate_into`` if given, which is then returned)
         epilogue "swiglu": rt.dtype [M,N/2], out[:,j] = silu(y[:,2j]) * y[:,2j+1]
         epilogue "geglu":  the same with the tanh form of gelu as the gate's activation
         epilogue "cast":   rt.dtype [M,N]
         epilogue "gelu" | "gelu_tanh" | "silu":  rt.dtype [M,N], the activation of every element
+        ``out`` ("none", "swiglu", "geglu" only): the tensor the result is written into instead of a new one.
         """
         if epilogue == "gelu" and self.tensor_core:
             return kernels.gemm_sm100(x, self.weight, bias=self.bias, epilogue="gelu")      # the activation in the product's epilogue
@@ -37,13 +38,13 @@ class Linear:
             y = kernels.gemm_sm100(x, self.weight, bias=self.bias) if self.tensor_core else kernels.gemm_simt(x, self.weight, bias=self.bias)
             return kernels.act_rows(y, self.rt.dtype, epilogue)
         if self.tensor_core:
-            return kernels.gemm_sm100(x, self.weight, bias=self.bias, accumulate_into=accumulate_into, epilogue=epilogue)
+            return kernels.gemm_sm100(x, self.weight, bias=self.bias, accumulate_into=accumulate_into, epilogue=epilogue, out=out)
         if epilogue == "none":
-            return kernels.gemm_simt(x, self.weight, bias=self.bias, out=accumulate_into,
+            return kernels.gemm_simt(x, self.weight, bias=self.bias, out=out if accumulate_into is None else accumulate_into,
                                      accumulate=accumulate_into is not None)
         y = kernels.gemm_simt(x, self.weight, bias=self.bias)
         if epilogue in ("swiglu", "geglu"):
-            return kernels.silu_mul_interleaved(y, self.rt.dtype, activation="silu" if epilogue == "swiglu" else "gelu_tanh")
+            return kernels.silu_mul_interleaved(y, self.rt.dtype, out=out, activation="silu" if epilogue == "swiglu" else "gelu_tanh")
         if epilogue == "cast":
             return y.to(self.rt.dtype)
         raise ValueError(f"unknown epilogue {epilogue!r}")

@@ -75,7 +75,11 @@ class PairedRotary(Part):
     the mixers that use it rotate inside their own prepare step (``kernels.headmix_prepare``) and ask for ``inv_freq``."""
     graph_safe = True
 
-    def __init__(self, rt, head_dim, rotary_dims=None, theta=10000.0):
+    def __init__(self, rt, head_dim, rotary_dims=None, theta=10000.0, scaling=None):
+        """``scaling`` {"factor", "original", "fast", "slow"} (optional): the pairs that turn fewer than ``slow`` times within
+        ``original`` positions are slowed down by ``factor``, those that turn more than ``fast`` times are left alone, a ramp
+        over the pair index between the two; cos and sin are then multiplied by ``amplitude`` = 0.1 ln(factor) + 1."""
+        import math
         import torch
         self.rt, self.head_dim, self.theta = rt, int(head_dim), float(theta)
         self.rotary_dims = self.head_dim if rotary_dims is None else int(rotary_dims)
@@ -84,6 +88,24 @@ class PairedRotary(Part):
             raise ConfigError(f"rotary encoding of {self.rotary_dims} channels does not fit heads of {self.head_dim}")
         i = torch.arange(self.rotary_dims // 2, dtype=torch.float64)
         freq = torch.pow(torch.tensor(self.theta, dtype=torch.float64), -2.0 * i / max(1, self.rotary_dims))
+        self.amplitude = 1.0
+        if scaling and self.rotary_dims:
+            from ..config.base import ConfigError
+            try:
+                factor, orig = float(scaling["factor"]), float(scaling["original"])
+                fast, slow = float(scaling["fast"]), float(scaling["slow"])
+            except (KeyError, TypeError, ValueError):
+                raise ConfigError("a rotation's scaling needs the numbers factor, original, fast and slow") from None
+            if not (factor > 0.0 and orig > 0.0 and fast > 0.0 and slow > 0.0 and self.theta > 1.0):
+                raise ConfigError("a rotation's scaling needs positive numbers and a base above one")
+
+            def pair_that_turns(times):      # the (fractional) pair index whose wave fits ``times`` times into ``orig`` positions
+                return self.rotary_dims * math.log(orig / (2.0 * math.pi * times)) / (2.0 * math.log(self.theta))
+            lo = max(math.floor(pair_that_turns(fast)), 0)
+            hi = min(math.ceil(pair_that_turns(slow)), self.rotary_dims - 1)
+            ramp = ((i - lo) / max(hi - lo, 0.001)).clamp(0.0, 1.0)
+            freq = freq / factor * ramp + freq * (1.0 - ramp)
+            self.amplitude = 0.1 * math.log(factor) + 1.0
         self.inv_freq = freq.to(torch.float32).to(rt.device)
 
 

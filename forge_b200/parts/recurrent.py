@@ -17,6 +17,11 @@ The rank of the decay's projection is read from the file's tensors (``rank`` is 
     q_t = silu(Wq h);  f_t = l + (1 - l) sigmoid(Wf h + b)  (l: a lower bound per channel);  v_t = Wv h
     S <- diag(f_t) S + (1 - f_t) v_t^T;   o_t = S^T q_t;   every head's o divided by its root mean square, times a weight per
     value channel that the heads share; projected back.  ``out_scale`` multiplies the mixer's output.
+
+"retention" (N heads of K key and V value channels, state [K, V], one fixed decay g_n per head, no softmax, no denominator):
+    q_t, k_t rotated by the position (a position part with ``inv_freq``; channel i paired with i + half), k_t times K^-1/2
+    S <- g_n S + k_t v_t^T;   o_t = S^T q_t;   every head's o divided by its root mean square (no weight), times silu(Wg h);
+    projected back.
 """
 import torch
 
@@ -177,6 +182,56 @@ class GatedWriteMixer(Part):
         self.o.forward(y, accumulate_into=residual)
 
 
+class RetentionMixer(Part):
+    graph_safe = True       # positions, request boundaries and state rows come from the batch's device tensors
+
+    def __init__(self, rt, hidden_size, num_heads, head_dim, decay, eps, position, v_head_dim=None, prefix="mix."):
+        from .base import build_part
+        if head_dim > 256:
+            raise ConfigError(f"the retention mixer takes heads of up to 256 key channels, not {head_dim}")
+        if len(decay) != num_heads:
+            raise ConfigError(f"retention: {len(decay)} decays for {num_heads} heads")
+        self.rt, self.hidden_size, self.num_heads, self.head_dim = rt, hidden_size, num_heads, head_dim
+        self.v_head_dim = head_dim if v_head_dim is None else v_head_dim
+        self.eps, self.prefix = float(eps), prefix
+        self.decay = torch.tensor([float(g) for g in decay], dtype=torch.float64).to(torch.float32).to(rt.device)
+        self.position = build_part("position", position, rt)
+        if not hasattr(self.position, "inv_freq"):
+            raise ConfigError("retention rotates inside its own scan and needs a position part with 'inv_freq'")
+        self.ones = torch.ones(self.v_head_dim, dtype=torch.float32, device=rt.device)       # the head norm has no weight
+
+    def sub_parts(self):
+        return [self.position]
+
+    def _n(self, short):
+        return self.prefix + short
+
+    def tensor_specs(self):
+        W, NK, NV = self.hidden_size, self.num_heads * self.head_dim, self.num_heads * self.v_head_dim
+        return {self._n("q"): TensorSpec((NK, W)), self._n("k"): TensorSpec((NK, W)), self._n("v"): TensorSpec((NV, W)),
+                self._n("g"): TensorSpec((NV, W)), self._n("o"): TensorSpec((W, NV))}
+
+    def bind(self, tensors):
+        # q, k, v and the gate read the same input: one product
+        self.proj = Linear(self._matrix(torch.cat([tensors[self._n(m)] for m in ("q", "k", "v", "g")], dim=0)), None, self.rt)
+        self.o = Linear(self._matrix(tensors[self._n("o")]), None, self.rt)
+
+    def cache_spec(self):
+        return StateSpec((self.num_heads * self.head_dim * self.v_head_dim,), torch.float32)
+
+    def forward(self, x, batch, cache, residual):
+        """Adds the mixer's output into ``residual``, or (``residual`` None) returns it as a new fp32 [T, W]."""
+        N, K, V = self.num_heads, self.head_dim, self.v_head_dim
+        NK, NV = N * K, N * V
+        p = self.proj.forward(x)                                     # fp32 [T, 2*N*K + 2*N*V]: q | k | v | g
+        freq = self.position.inv_freq
+        o = kernels.retention_scan((p, 0), (p, NK), (p, 2 * NK), batch, freq if freq.numel() else None, K ** -0.5, self.decay,
+                                   cache.state, N, K, V)
+        y = kernels.head_finish(o, self.ones, (p, 2 * NK + NV), N, V, self.eps, "silu", self.rt.dtype)
+        return self.o.forward(y, accumulate_into=residual)
+
+
+register_part("mixer", "retention", RetentionMixer, replace=True)
 register_part("mixer", "gated_write", GatedWriteMixer, replace=True)
 register_part("mixer", "wkv", WKVMixer, replace=True)
 register_part("mixer", "general_delta", GeneralDeltaMixer, replace=True)

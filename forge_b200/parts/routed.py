@@ -1,0 +1,82 @@
+"""A feed-forward made of many small gated feed-forwards ("experts"), of which a router picks ``top`` per token:
+
+    s = sigmoid(Wr x)  (or softmax(Wr x));   the ``top`` largest s choose the experts (the lower index wins a tie)
+    y = sum over the chosen e of s_e * Wdown_e (silu(Wgate_e x) * (Wup_e x))          (s_e divided by their sum with ``renormalize``)
+
+The router's arithmetic is fp32.  Steps of few tokens, and every step that a CUDA graph replays, take each (token, expert)
+pair on its own with everything read from device memory; steps of many tokens rank the pairs by expert, run every
+expert's rows through the ordinary matrix products, and add a token's experts up in the router's order.
+"""
+import torch
+
+from .. import kernels
+from ..config.base import ConfigError
+from ..weights.loader import TensorSpec
+from .base import Part, register_part
+from .linear import Linear
+
+
+class RoutedExperts(Part):
+    graph_safe = True
+    SORTED_FROM = 128          # tokens in a step from which the pairs are ranked by expert
+
+    def __init__(self, rt, hidden_size, intermediate_size, experts, top, score="sigmoid", renormalize=False, prefix="mlp."):
+        if not 1 <= top <= experts:
+            raise ConfigError(f"routed feed-forward: {top} of {experts} experts")
+        if score not in ("sigmoid", "softmax"):
+            raise ConfigError(f"routed feed-forward: scores are 'sigmoid' or 'softmax', not {score!r}")
+        self.rt, self.hidden_size, self.intermediate_size = rt, hidden_size, intermediate_size
+        self.experts, self.top, self.score, self.renormalize, self.prefix = experts, top, score, bool(renormalize), prefix
+
+    def _n(self, short):
+        return self.prefix + short
+
+    def tensor_specs(self):
+        W, F = self.hidden_size, self.intermediate_size
+        specs = {}
+        for e in range(self.experts):
+            specs.update({self._n(f"e{e}.gate"): TensorSpec((F, W)), self._n(f"e{e}.up"): TensorSpec((F, W)),
+                          self._n(f"e{e}.down"): TensorSpec((W, F))})
+        specs[self._n("router")] = TensorSpec((self.experts, W))
+        return specs
+
+    def bind(self, tensors):
+        W, F, E = self.hidden_size, self.intermediate_size, self.experts
+        self.router = self._vector_f32(tensors[self._n("router")])                     # fp32 whatever the runtime
+        # one tensor per kind for all experts; gate and up rows alternate so that the product's epilogue sees (gate, up) pairs
+        gu = torch.stack([torch.stack([tensors[self._n(f"e{e}.gate")], tensors[self._n(f"e{e}.up")]], dim=1).reshape(2 * F, W)
+                          for e in range(E)])
+        self.gate_up = self._matrix(gu)                                                # [E, 2F, W]
+        self.down = self._matrix(torch.stack([tensors[self._n(f"e{e}.down")] for e in range(E)]))      # [E, W, F]
+        self.gate_up_of = [Linear(self.gate_up[e], None, self.rt) for e in range(E)]   # views, no copies
+        self.down_of = [Linear(self.down[e], None, self.rt) for e in range(E)]
+
+    def _ranked(self, x, idx, wts):
+        """The path of many tokens.  The number of rows of every expert has to be known on the host: one wait per layer."""
+        T, W, F = x.shape[0], self.hidden_size, self.intermediate_size
+        xg, counts, dest = kernels.moe_sort(x, idx, self.experts)
+        counts = counts.tolist()
+        act = kernels.new_tensor((T * self.top, F), self.rt.dtype, x.device)
+        ys = kernels.new_tensor((T * self.top, W), torch.float32, x.device)
+        off = 0
+        for e, n in enumerate(counts):
+            if n:
+                self.gate_up_of[e].forward(xg[off:off + n], epilogue="swiglu", out=act[off:off + n])
+                self.down_of[e].forward(act[off:off + n], out=ys[off:off + n])
+                off += n
+        return kernels.moe_combine(ys, dest, wts)
+
+    def forward(self, x, residual):
+        """Adds the output into ``residual`` fp32 [T, W], or (``residual`` None) returns it as a new fp32 [T, W]."""
+        idx, wts = kernels.moe_route(x, self.router, self.top, softmax=self.score == "softmax", renorm=self.renormalize)
+        if x.shape[0] >= self.SORTED_FROM and not torch.cuda.is_current_stream_capturing():
+            y = self._ranked(x, idx, wts)
+        else:
+            y = kernels.moe_pairs(x, idx, wts, self.gate_up, self.down)
+        if residual is None:
+            return y
+        residual.add_(y)
+        return residual
+
+
+register_part("feed_forward", "routed_experts", RoutedExperts, replace=True)

@@ -39,6 +39,11 @@ def random_tensors(config, seed=0, std=0.02, embed_std=None, norm_std=0.0, bias_
         elif spec.role == "lambda_part":      # vectors whose pairwise dot products are exponentiated: keep those of order 1/2
             n = max(1, int(torch.tensor(spec.shape).prod()))
             out[name] = (torch.randn(spec.shape, generator=gen, dtype=torch.float32, device=device) * (0.7 / n ** 0.25)).to(dtype)
+        elif spec.role == "norm_offset":      # a norm weight stored as its distance from one
+            t = torch.zeros(spec.shape, dtype=torch.float32, device=device)
+            if norm_std:
+                t += torch.randn(spec.shape, generator=gen, dtype=torch.float32, device=device) * norm_std
+            out[name] = t
         elif spec.role == "norm":
             t = torch.ones(spec.shape, dtype=torch.float32, device=device)
             if norm_std:
