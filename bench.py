@@ -162,7 +162,7 @@ def main():
     ap.add_argument("--no-points", action="store_true", help="skip batch 1 / 64 and the prefill")
     ap.add_argument("--no-shapes", action="store_true", help="skip the Llama-3-8B and Qwen2.5-7B shaped points")
     ap.add_argument("--block-size", type=int, default=64, help="tokens per cache page (named in config)")
-    ap.add_argument("--design", default=None, choices=["zatupel", "tidenex"],
+    ap.add_argument("--design", default=None, choices=["zatupel", "tidenex", "tuzavik"],
                     help="instead of the default workload: prefill and decode speed of that design at a few layer sizes, "
                          "beside the LLaMA decoder of equal width, depth and head counts")
     a = ap.parse_args()
@@ -531,8 +531,85 @@ class TidenexBench(ShapeBench):
         return flops
 
 
+def tuzavik_shape(width, layers, heads, dim, ff, state_heads, state_dim, vocab, **_):
+    """A Tuzavik configuration at a real model's layer sizes: latent attention (``heads`` heads of ``dim`` unrotated, dim/2 rotated and
+    ``dim`` value channels over a latent of 4*dim channels, queries through a latent of 3/4 of the width), two retention layers and a
+    latent attention that reads the first one's rows, in turn; the feed-forward is dense and routed in turn (8 experts of half the
+    dense width, 2 a token, so that a token passes through as many feed-forward weights as in the other decoders)."""
+    rot = {"dims": dim // 2, "base": 10000.0, "scaling": {"factor": 8.0, "original": 1024, "fast": 32.0, "slow": 1.0}}
+    lat = lambda src: {"type": "latent_attention", "mixer": dict({"heads": heads, "dim": dim, "rot_dim": dim // 2, "vdim": dim, "kv_rank": 4 * dim,
+                                                                 "q_rank": 3 * width // 4, "scale": (dim + dim // 2) ** -0.5, "rot": rot},
+                                                                **({} if src is None else {"kv_from": src}))}
+    ret = {"type": "retention", "mixer": {"heads": state_heads, "dim": state_dim, "vdim": state_dim, "rot": {"dims": state_dim, "base": 10000.0},
+                                          "decay": [1.0 - 2.0 ** (-5.0 - 5.0 * n / max(1, state_heads - 1)) for n in range(state_heads)]}}
+    dense = {"kind": "dense", "ff": ff}
+    moe = {"kind": "moe", "expert": {"ff": ff // 2}, "router": {"experts": 8, "top": 2}}
+    out = []
+    for i in range(layers):
+        kind = i % 4
+        layer = lat(None) if kind == 0 else (lat(i - 3) if kind == 3 else ret)
+        out.append(dict(layer, mlp=dense if i % 2 == 0 else moe))
+    return {"architecture": "Tuzavik", "vocab": vocab, "width": width, "norm": {"eps": 1e-5}, "residual_mult": 0.5, "logit_scale": 0.5,
+            "embedding": {"bigram": {"buckets": 8191, "mul_prev": 31, "mul_cur": 7}}, "max_positions": 8192, "layers": out}
+
+
+def tuzavik_matmul_params(cfg, experts_read=None):
+    """Matrix elements of all layers that a token passes through (``experts_read`` None: its ``top`` experts) or that a step
+    reads (``experts_read``: how many experts of a routed layer), and of the head."""
+    W, total = cfg.width, 0
+    for layer in cfg.layers:
+        m = layer["mixer"]
+        if layer["type"] == "retention":
+            NK, NV = m["heads"] * m["dim"], m["heads"] * m.get("vdim", m["dim"])
+            total += W * (2 * NK + 2 * NV) + W * NV
+        else:
+            H, D, R, E, C, Cq = m["heads"], m["dim"], m["rot_dim"], m["vdim"], m["kv_rank"], m["q_rank"]
+            total += W * Cq + Cq * H * (D + R) + H * D * C + H * E * C + W * H * E + (0 if m.get("kv_from") is not None else W * (C + R))
+        mlp = layer.get("mlp")
+        if mlp and mlp["kind"] == "dense":
+            total += 3 * W * mlp["ff"]
+        elif mlp:
+            n = mlp["router"]["top"] if experts_read is None else min(mlp["router"]["experts"], experts_read)
+            total += 3 * W * mlp["expert"]["ff"] * n + W * mlp["router"]["experts"]
+    return total, cfg.vocab * W
+
+
+class TuzavikBench(ShapeBench):
+    """ShapeBench's measurements for a Tuzavik configuration: only bytes and FLOPs are counted otherwise."""
+
+    def decode_bytes(self, B, ctx):
+        """Every matrix that the step reads once (of a routed layer the experts that B tokens can choose), and per request the latent
+        rows of every layer that caches some (a layer that reads another's rows reads them again) and the state matrices, read and
+        written."""
+        cfg = self.cfg
+        top = max([l["mlp"]["router"]["top"] for l in cfg.layers if l.get("mlp") and l["mlp"]["kind"] == "moe"] or [1])
+        layers, head = tuzavik_matmul_params(cfg, experts_read=B * top)
+        total = 2 * (layers + head)
+        for layer in cfg.layers:
+            m = layer["mixer"]
+            if layer["type"] == "retention":
+                total += B * 2 * 4 * m["heads"] * m["dim"] * m.get("vdim", m["dim"])
+            else:
+                total += B * ctx * (m["kv_rank"] + m["rot_dim"]) * 2
+        return total
+
+    def prefill_flops(self, T):
+        """Products, the attention as the design states it (per visible pair and head: scores over dim + rot_dim channels, values of
+        vdim; the engine's absorbed form executes kv_rank + rot_dim and kv_rank instead), 4 FLOPs per state element and token."""
+        cfg = self.cfg
+        layers, head = tuzavik_matmul_params(cfg)
+        flops, pairs = 2 * T * layers + 2 * head, T * (T + 1) // 2
+        for layer in cfg.layers:
+            m = layer["mixer"]
+            if layer["type"] == "retention":
+                flops += 4 * T * m["heads"] * m["dim"] * m.get("vdim", m["dim"])
+            else:
+                flops += 2 * pairs * m["heads"] * (m["dim"] + m["rot_dim"] + m["vdim"])
+        return flops
+
+
 def design_arm(a):
-    """Prefill and decode speed of the Zatupel or Tidenex design at a few layer sizes (random weights), each beside the LLaMA decoder
+    """Prefill and decode speed of the Zatupel, Tidenex or Tuzavik design at a few layer sizes (random weights), each beside the LLaMA decoder
     of the same width, depth, head counts and feed-forward width run the same way: decode device-timed at batch 1, 8 and
     64 after 512-token prompts, one prompt step of 2,048 tokens.  One JSON line."""
     import torch
@@ -560,6 +637,8 @@ def design_arm(a):
         arms = [("zatupel", zatupel_shape(**z), ZatupelBench), ("llama", llama, ShapeBench)]
         if a.design == "tidenex":         # beside the hybrid whose kernels are the nearest, and the plain decoder
             arms.insert(0, ("tidenex", tidenex_shape(**z), TidenexBench))
+        if a.design == "tuzavik":         # beside the design whose state scan and attention kernels are the nearest, and the plain decoder
+            arms = [("tuzavik", tuzavik_shape(**z), TuzavikBench), ("tidenex", tidenex_shape(**z), TidenexBench), arms[1]]
         for arch, shape, maker in arms:
             b = maker(shape, PROMPT_LEN, 64, steps, a.warmup, a.block_size, prefill_tokens=PREFILL_TOKENS)
             r = {}

@@ -65,3 +65,26 @@ def test_the_other_design_option_too():
     specs = Model(cfg.plan(), Runtime(torch.device("cpu"), torch.bfloat16)).tensor_specs()
     matrices = sum(s.shape[0] * s.shape[1] for n, s in specs.items() if len(s.shape) == 2 and s.required and n != "embed")
     assert layers == matrices and head == 300 * 256
+
+
+def test_the_third_design_option_too():
+    rc, lines = _run("--design", "tuzavik", "--gpus", "2")
+    assert rc == 2 and len(lines) == 1 and "single-GPU" in json.loads(lines[0])["error"]
+    sys.path.insert(0, ROOT)
+    import bench
+    import torch
+    from forge_b200.config import config_from_dict
+    from forge_b200.engine.model import Model
+    from forge_b200.parts import Runtime
+    z = dict(width=256, layers=5, heads=8, kv_heads=2, dim=32, ff=512, state_heads=4, state_dim=32, rank=16, window=64, vocab=300)
+    cfg = config_from_dict(bench.tuzavik_shape(**z))
+    assert [l["type"] for l in cfg.layers] == ["latent_attention", "retention", "retention", "latent_attention", "latent_attention"]
+    assert [l["mixer"].get("kv_from") for l in cfg.layers] == [None, None, None, 0, None]
+    assert [l["mlp"]["kind"] for l in cfg.layers] == ["dense", "moe", "dense", "moe", "dense"]
+    # counted from the configuration alone with every expert read, the matrices are what the model's own tensor list holds
+    layers, head = bench.tuzavik_matmul_params(cfg, experts_read=8)
+    specs = Model(cfg.plan(), Runtime(torch.device("cpu"), torch.bfloat16)).tensor_specs()
+    matrices = sum(s.shape[0] * s.shape[1] for n, s in specs.items() if len(s.shape) == 2 and s.required and n not in ("embed", "bigram", "head"))
+    assert layers == matrices and head == 300 * 256
+    per_token, _ = bench.tuzavik_matmul_params(cfg)
+    assert layers - per_token == 2 * 6 * 3 * 256 * 256                    # six of eight experts of two routed layers
