@@ -82,6 +82,9 @@ _SIGNATURES = {
         "forge_latent_prepare": [_P, _I, _P, _P, _P, _F, _P, _P, _P, _P, _I, _I, _I, _I, _I, _F, _P],
         "forge_head_linear": [_P, _I, _LL, _I, _P, _P, _I, _LL, _I, _P, _P, _F, _I, _I, _I, _I, _I, _P],
         "forge_latent_attention": [_P] * 8 + [_I] * 8 + [_F, _I, _I, _P],
+        "forge_latent_mma_supports": [_I] * 4,
+        "forge_latent_mma_heads": [_I],
+        "forge_latent_attention_mma": [_P] * 9 + [_I, _P] + [_I] * 7 + [_F, _P],
     },
     "moe": {
         "forge_moe_route": [_P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _P],
@@ -107,7 +110,7 @@ _libs = {}
 _CHECK_ENTRIES = {"core": ["forge_checks_configure_rope", "forge_checks_configure_attention_simt"],
                   "mixers": ["forge_checks_configure_attention_headmix", "forge_checks_configure_attention_headmix_mma",
                              "forge_checks_configure_attention_scored", "forge_checks_configure_attention_scored_mma"],
-                  "latent": ["forge_checks_configure_attention_latent"],
+                  "latent": ["forge_checks_configure_attention_latent", "forge_checks_configure_attention_latent_mma"],
                   "gemm_sm100": ["forge_checks_configure_gemm_sm100"],
                   "attention_mma": ["forge_checks_configure_attention_mma", "forge_checks_configure_attention_decode_stream"],
                   "attention_sm100": ["forge_checks_configure_attention_sm100"]}
@@ -1097,6 +1100,28 @@ def latent_attention(q, cache, group_batch, batch, H, C, R, page_size, scale):
     T = q.shape[0]
     if cache.dtype != q.dtype:
         raise KernelError("latent_attention: q and cache dtypes differ")
+    if q.dtype == torch.bfloat16 and _TENSOR_CORE_ATTENTION and lib.forge_latent_mma_supports.fn(H, C, R, page_size):
+        # tensor cores: rows of (token, head) over the same tiles of latent rows
+        HG = lib.forge_latent_mma_heads.fn(H)
+        t0, tn, tiles = headmix_plan(batch, max(1, 64 // HG), q.device)
+        nsplit = 1
+        if getattr(batch, "decode_only", False):
+            # a step of single tokens brings T * (head groups) * (value chunks) CTAs: deal a request's tiles out to several, up to
+            # one CTA per SM, as far as the longest context (the graph's bucket) has tiles
+            ctas = T * -(-H // HG) * -(-C // 256)
+            nsplit = max(1, min(8, -(-batch.max_context // 64), _sm_count(q.device) // max(1, ctas)))
+        u = new_tensor((nsplit, T, H, C), torch.float32, q.device) if nsplit > 1 else None
+        part_ml = new_tensor((nsplit, T, H, 2), torch.float32, q.device) if nsplit > 1 else None
+        out = new_tensor((T, H * C), q.dtype, q.device)
+        _check(lib, lib.forge_latent_attention_mma(
+            _need(q, "q", torch.bfloat16, 2), _need(cache, "cache", torch.bfloat16), _need(group_batch.block_table, "block_table", torch.int32, 2),
+            _need(batch.tok_req, "tok_req", torch.int32), _need(batch.positions, "positions", torch.int32), _opt(t0, "tile_t0", torch.int32),
+            _opt(tn, "tile_n", torch.int32), _opt(u, "u", torch.float32), _opt(part_ml, "part_ml", torch.float32), nsplit,
+            _need(out, "out", torch.bfloat16), T, tiles, H, C, R, page_size, group_batch.block_table.shape[1], float(scale), _stream()),
+            "latent_attention_mma")
+        if nsplit > 1:
+            count_launches(1)      # the kernel that puts the runs of tiles together
+        return out
     single = getattr(batch, "decode_only", False) or batch.num_tokens == batch.num_requests
     TQ, HG = latent_tile_shape(H, C, R, single_tokens=single)
     t0, tn, tiles = headmix_plan(batch, TQ, q.device)

@@ -34,7 +34,7 @@ LIBRARIES = {
     "mixers": ["attention_headmix.cu", "attention_headmix_mma.cu", "attention_scored.cu", "attention_scored_mma.cu", "recurrent.cu"],
     # attention over one latent row per token shared by all heads (keys and values per head are never formed), and the
     # per-head products around it
-    "latent": ["attention_latent.cu"],
+    "latent": ["attention_latent.cu", "attention_latent_mma.cu"],
     # routed experts: router, the path by (token, expert) pairs, the sorted path's ranking, gathering and adding up
     "moe": ["moe.cu"],
     # all layers of a decode step in one persistent kernel (tcgen05 + TMA weight stream, attention inside)

@@ -188,7 +188,53 @@ def case(name):
             x.copy_(x0)
             state_scan("gated_write", (r, 0), None, (v, 0), (x, 0), fb, state, batch, N, K, a0=low, KV=K)
         return run, 3 * T * N * K * 4, 4 * T * N * K * K
-    raise SystemExit(f"unknown case {name!r}; known: scored_attention_prefill scored_attention_decode distance_attention_prefill state_scan_gated headmix_attention_prefill headmix_attention_decode state_scan_wkv state_scan_delta "
+    if name in ("latent_attention_prefill", "latent_attention_decode", "latent_attention_prefill_512"):
+        # attention over latent rows: 32 heads whose absorbed queries (256 + 32 channels; 512 + 64 in the last case) read the same
+        # rows; one prompt of 2,048 tokens, or 8 requests of 1,023 cached tokens and one new one.  FLOPs as executed: per visible
+        # (token, row) pair and head 2 (C + R) for the score and 2 C for the weighted sum
+        from forge_b200.kernels import latent_attention
+        ps = 64
+        Hh, C, R = (32, 512, 64) if name.endswith("512") else (32, 256, 32)
+        reqs = [(1023, 1)] * 8 if name.endswith("decode") else [(0, 2048)]
+        pages_per = [-(-(c + n) // ps) for c, n in reqs]
+        table = torch.full((len(reqs), max(pages_per)), -1, dtype=torch.int32)
+        q_start, nxt = [0], 0
+        for s_, n in enumerate(pages_per):
+            table[s_, :n] = torch.arange(nxt, nxt + n, dtype=torch.int32)
+            nxt += n
+            q_start.append(q_start[-1] + reqs[s_][1])
+        T = q_start[-1]
+        i32 = lambda x: torch.tensor(x, dtype=torch.int32, device=DEV)
+        batch = SimpleNamespace(num_requests=len(reqs), num_tokens=T, host_q_start=q_start, attention_plan={},
+                                tok_req=i32([s_ for s_, (c, n) in enumerate(reqs) for _ in range(n)]),
+                                positions=i32([c + j for c, n in reqs for j in range(n)]))
+        if name.endswith("decode"):
+            batch.decode_only, batch.max_context = True, 1024
+        g = SimpleNamespace(block_table=table.to(DEV))
+        q, cache = _bf16(T, Hh * (C + R), scale=0.3), _bf16(nxt, ps * (C + R))
+        pairs = sum(c + j + 1 for c, n in reqs for j in range(n))
+        return (lambda: latent_attention(q, cache, g, batch, Hh, C, R, ps, (C + R) ** -0.5)), \
+            pairs * (C + R) * 2 // max(1, T // len(reqs)), 2 * pairs * Hh * (2 * C + R)
+    if name == "retention_scan":
+        # the retention recurrence alone: one request of 1,024 tokens, 32 heads of 64 key and 64 value channels (4 FLOPs per
+        # state element and token), with the kernel that rotates q and k in front of it
+        from forge_b200.kernels import retention_scan
+        T, N, K = 1024, 32, 64
+        mk = lambda: torch.randn(T, N * K, device=DEV) * 0.5
+        qq, kk, v = mk(), mk(), mk()
+        q0, k0 = qq.clone(), kk.clone()
+        freq = torch.pow(torch.tensor(10000.0), -torch.arange(K // 2, dtype=torch.float32) * 2 / K).to(DEV)
+        decay = torch.linspace(0.97, 0.999, N, device=DEV)
+        state = torch.zeros(2, N * K * K, device=DEV)
+        i32 = lambda z: torch.tensor(z, dtype=torch.int32, device=DEV)
+        batch = SimpleNamespace(q_start=i32([0, T]), slots=i32([1]), num_requests=1, positions=torch.arange(T, dtype=torch.int32, device=DEV))
+
+        def run():
+            qq.copy_(q0)            # the scan rotates q and k in place
+            kk.copy_(k0)
+            retention_scan((qq, 0), (kk, 0), (v, 0), batch, freq, K ** -0.5, decay, state, N, K, K)
+        return run, 3 * T * N * K * 4, 4 * T * N * K * K
+    raise SystemExit(f"unknown case {name!r}; known: latent_attention_prefill latent_attention_prefill_512 latent_attention_decode retention_scan scored_attention_prefill scored_attention_decode distance_attention_prefill state_scan_gated headmix_attention_prefill headmix_attention_decode state_scan_wkv state_scan_delta "
                      "gemm_decode_gateup gemm_decode_down gemm_decode_lmhead gemm_prefill_qkv "
                      "gemm_prefill_gateup "
                      "gemm_prefill_qkv_rope gemm_prefill_down attention_decode attention_decode_fused attention_decode_stream attention_prefill "

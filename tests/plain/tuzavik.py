@@ -147,12 +147,20 @@ def gated_ff(x, w_gate, w_up, w_down):
     return (silu(x @ w_gate.t()) * (x @ w_up.t())) @ w_down.t()
 
 
-def routed_ff(x, w, mlp):
+def routed_ff(x, w, mlp, margins=None, chosen=None):
     """Every token goes through the ``top`` experts with the largest sigmoid(router logits); their outputs are added with
-    those sigmoids as weights, not renormalised."""
+    those sigmoids as weights, not renormalised.  ``margins``: a list that receives, per token, how far the last chosen expert's
+    router logit lies above the first one left out, as a fraction of the largest logit's size (inf when all are chosen).
+    ``chosen`` [T, top]: experts to take instead of the router's own choice (their weights are still the router's scores)."""
     n, top = mlp["router"]["experts"], mlp["router"]["top"]
-    score = torch.sigmoid(x @ w["router"].t())
-    chosen = torch.topk(score, top, dim=-1).indices
+    z = x @ w["router"].t()
+    score = torch.sigmoid(z)
+    if margins is not None:
+        zs = z.sort(dim=-1, descending=True).values
+        margins.append(torch.full((x.shape[0],), float("inf"), dtype=x.dtype) if top == n else
+                       (zs[:, top - 1] - zs[:, top]) / z.abs().amax(dim=-1).clamp_min(1e-30))
+    if chosen is None:
+        chosen = torch.topk(score, top, dim=-1).indices
     out = torch.zeros(x.shape[0], w["e0.down"].shape[0], dtype=x.dtype)
     for t in range(x.shape[0]):
         for e in chosen[t].tolist():
@@ -164,12 +172,14 @@ def _sub(tensors, prefix):
     return {k[len(prefix):]: v for k, v in tensors.items() if k.startswith(prefix)}
 
 
-def forward(cfg, tensors, tokens, dtype=torch.float64, streams=None):
-    """Logits [T, vocab] of one sequence.  ``streams``: a list that receives the residual stream after every layer."""
+def forward(cfg, tensors, tokens, dtype=torch.float64, streams=None, margins=None, choices=None):
+    """Logits [T, vocab] of one sequence.  ``streams``: a list that receives the residual stream after every layer;
+    ``margins``: one that receives every routed layer's margins (see routed_ff); ``choices``: per routed layer, in order, the
+    experts to take instead of the router's own."""
     w = {k: torch.as_tensor(v).to(dtype) for k, v in tensors.items() if torch.as_tensor(v).dtype.is_floating_point}
     eps, mult = float(cfg["norm"]["eps"]), float(cfg.get("residual_mult", 1.0))
     x = embed(list(tokens), w["embed"], w.get("bigram"), cfg.get("embedding"))
-    kept = {}
+    kept, routed = {}, 0
     for i, layer in enumerate(cfg["layers"]):
         p, m = f"l{i}.", layer["mixer"]
         h = norm_around_zero(x, w[p + "norm1"], eps)
@@ -183,7 +193,11 @@ def forward(cfg, tensors, tokens, dtype=torch.float64, streams=None):
         if mlp is not None:
             h = norm_around_zero(x, w[p + "norm2"], eps)
             mw = _sub(w, p + "mlp.")
-            y = gated_ff(h, mw["gate"], mw["up"], mw["down"]) if mlp["kind"] == "dense" else routed_ff(h, mw, mlp)
+            if mlp["kind"] == "dense":
+                y = gated_ff(h, mw["gate"], mw["up"], mw["down"])
+            else:
+                y = routed_ff(h, mw, mlp, margins, None if choices is None else choices[routed])
+                routed += 1
             x = x + mult * norm_around_zero(y, w[p + "norm2b"], eps)
         if streams is not None:
             streams.append(x.clone())

@@ -47,7 +47,7 @@ TUZ = {
                      _dense(_ret(2, 6, 14, [0.97, 0.8], 6, 5000.0), None),
                      _moe(_lat(2, 12, 4, 8, 20, 16, 0.3, 50.0, scaling=(4.0, 64, 8.0, 2.0), kv_from=1), 100, 3, 3),
                      _dense(_lat(5, 4, 4, 6, 20, 12, 0.7, 50.0, scaling=(4.0, 64, 8.0, 2.0), kv_from=1), 72)]},
-    "Y": {"architecture": "Tuzavik", "vocab": 130, "width": 48, "norm": {"eps": 1e-2}, "residual_mult": 1.3, "logit_scale": 0.8,
+    "Y": {"architecture": "Tuzavik", "vocab": 130, "width": 48, "norm": {"eps": 1e-2}, "residual_mult": 1.2, "logit_scale": 0.8,
           "layers": [_dense(_lat(2, 16, 8, 8, 40, 10, 0.25, 10000.0), 40),
                      _moe(_ret(1, 40, 24, [0.99], None, None), 16, 4, 2),
                      _dense(_lat(4, 6, 10, 20, 12, 36, 0.35, 77.0, scaling=(16.0, 40, 4.0, 1.0)), None)]},
@@ -60,7 +60,7 @@ TUZ = {
                      _dense(_ret(2, 128, 32, [0.98, 0.875], 128, 10000.0), 384)]},
 }
 SEEDS = {"X": 31, "Y": 32, "Z": 33}
-STDS = {"X": dict(std=0.14, embed_std=0.6, norm_std=0.2), "Y": dict(std=0.2, embed_std=0.8, norm_std=0.2),
+STDS = {"X": dict(std=0.14, embed_std=0.6, norm_std=0.2), "Y": dict(std=0.16, embed_std=0.8, norm_std=0.2),
         "Z": dict(std=0.08, embed_std=0.6, norm_std=0.2)}
 LENGTHS = {"X": [70, 129, 33, 150, 64, 97], "Y": [90, 47, 16, 140, 81], "Z": [160, 20, 131, 45]}
 
