@@ -11,6 +11,8 @@
 //
 // Router arithmetic is fp32 whatever the activations' type.  Every sum has a fixed order: a dot product is dealt to the
 // lanes of a warp by index and summed by the butterfly, a token's experts are added in the order of their scores.
+#include <algorithm>
+#include <type_traits>
 #include "common.cuh"
 
 namespace {
@@ -140,6 +142,110 @@ moe_pair_down_kernel(const TA* __restrict__ act, const TW* __restrict__ Wd, cons
     }
 }
 
+constexpr int kGroupTokens = 8;           // input rows that share one pass over an expert's weight rows
+
+// The same sums as the two kernels above, expert by expert, so that a weight row is read once for up to 8 of the expert's
+// pairs instead of once per pair: grid (E, ceil(N / 32)).  A CTA lists the pairs that chose its expert (in order), stages
+// their input rows in shared memory eight at a time and gives every warp 8 of the 32 output rows.
+//   GATED:  out[p, j] = act_fn(Wa[e][j] . in[p / in_div]) * (Wb[e][j] . in[p / in_div])   (out of the activations' type)
+//   else:   out[p, j] = Wa[e][j] . in[p]                                                   (out fp32; a later kernel weighs and adds)
+// Row j of expert e lies at e * expert_stride + j * ld.  A dot product is dealt to the lanes and summed exactly as lane_dot
+// does, so a pair's numbers do not depend on which of the paths took it.
+template <typename TA, typename TW, bool GATED>
+__global__ void __launch_bounds__(128)
+moe_expert_rows_kernel(const TA* __restrict__ in, int in_div, const TW* __restrict__ Wa, const TW* __restrict__ Wb, long long ld,
+                       long long expert_stride, const int32_t* __restrict__ idx, void* __restrict__ out_, int P, int K, int N, int nt_max) {
+    extern __shared__ __align__(16) unsigned char moe_smem[];
+    __shared__ int s_count;
+    forge::pdl_launch_dependents();
+    forge::pdl_wait();
+    float* xs = reinterpret_cast<float*>(moe_smem);                        // [nt_max][K]
+    int* plist = reinterpret_cast<int*>(xs + (size_t)nt_max * K);          // [P]
+    const int e = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    if (warp == 0) {                                                       // the expert's pairs, in order
+        int n = 0;
+        for (int p0 = 0; p0 < P; p0 += 32) {
+            const bool mine = p0 + lane < P && idx[p0 + lane] == e;
+            const unsigned m = __ballot_sync(0xffffffffu, mine);
+            if (mine) plist[n + __popc(m & ((1u << lane) - 1u))] = p0 + lane;
+            n += __popc(m);
+        }
+        if (lane == 0) s_count = n;
+    }
+    __syncthreads();
+    const int count = s_count;
+    const TW* wa = Wa + (size_t)e * expert_stride;
+    const TW* wb = GATED ? Wb + (size_t)e * expert_stride : nullptr;
+    const bool vec = std::is_same<TW, __nv_bfloat16>::value && (K & 7) == 0 && (ld & 7) == 0 && (expert_stride & 7) == 0 &&
+                     (((uintptr_t)Wa) & 15) == 0 && (!GATED || (((uintptr_t)Wb) & 15) == 0);
+    for (int g0 = 0; g0 < count; g0 += nt_max) {
+        const int nt = min(nt_max, count - g0);
+        __syncthreads();                                                   // the group before is done with xs
+        for (int i = threadIdx.x; i < nt * K; i += 128) {
+            const int n = i / K, c = i - n * K;
+            xs[i] = forge::to_float(in[(size_t)(plist[g0 + n] / in_div) * K + c]);
+        }
+        __syncthreads();
+        for (int jj = 0; jj < kPairOutputs / 4; ++jj) {
+            const int j = blockIdx.y * kPairOutputs + warp * (kPairOutputs / 4) + jj;
+            if (j >= N) break;
+            float a[kGroupTokens], b[kGroupTokens];
+#pragma unroll
+            for (int n = 0; n < kGroupTokens; ++n) a[n] = b[n] = 0.f;
+            const TW* ra = wa + (size_t)j * ld;
+            const TW* rb = GATED ? wb + (size_t)j * ld : nullptr;
+            if (vec) {
+                for (int c = lane * 8; c < K; c += 256) {
+                    const uint4 raw_a = *reinterpret_cast<const uint4*>(ra + c);
+                    uint4 raw_b = raw_a;
+                    if (GATED) raw_b = *reinterpret_cast<const uint4*>(rb + c);
+                    const __nv_bfloat162* pa = reinterpret_cast<const __nv_bfloat162*>(&raw_a);
+                    const __nv_bfloat162* pb = reinterpret_cast<const __nv_bfloat162*>(&raw_b);
+                    float fa[8], fb[8];
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) {
+                        const float2 u = __bfloat1622float2(pa[i]), v = __bfloat1622float2(pb[i]);
+                        fa[2 * i] = u.x; fa[2 * i + 1] = u.y; fb[2 * i] = v.x; fb[2 * i + 1] = v.y;
+                    }
+#pragma unroll
+                    for (int n = 0; n < kGroupTokens; ++n) {
+                        if (n >= nt) break;
+                        const float4 x0 = *reinterpret_cast<const float4*>(xs + (size_t)n * K + c);
+                        const float4 x1 = *reinterpret_cast<const float4*>(xs + (size_t)n * K + c + 4);
+                        const float xv[8] = {x0.x, x0.y, x0.z, x0.w, x1.x, x1.y, x1.z, x1.w};
+#pragma unroll
+                        for (int i = 0; i < 8; ++i) {
+                            a[n] = fmaf(fa[i], xv[i], a[n]);
+                            if (GATED) b[n] = fmaf(fb[i], xv[i], b[n]);
+                        }
+                    }
+                }
+            } else {
+                for (int c = lane; c < K; c += 32) {
+                    const float fa = forge::to_float(ra[c]), fb = GATED ? forge::to_float(rb[c]) : 0.f;
+#pragma unroll
+                    for (int n = 0; n < kGroupTokens; ++n) {
+                        if (n >= nt) break;
+                        a[n] = fmaf(fa, xs[(size_t)n * K + c], a[n]);
+                        if (GATED) b[n] = fmaf(fb, xs[(size_t)n * K + c], b[n]);
+                    }
+                }
+            }
+#pragma unroll
+            for (int n = 0; n < kGroupTokens; ++n) {
+                if (n >= nt) break;
+                const float sa = forge::warp_sum(a[n]);
+                const float sb = GATED ? forge::warp_sum(b[n]) : 0.f;
+                if (lane == 0) {
+                    const size_t o = (size_t)plist[g0 + n] * N + j;
+                    if (GATED) reinterpret_cast<TA*>(out_)[o] = forge::from_float<TA>(siluf(sa) * sb);
+                    else reinterpret_cast<float*>(out_)[o] = sa;
+                }
+            }
+        }
+    }
+}
+
 // One CTA per expert walks all pairs in order: rank[p] = how many earlier pairs chose the same expert; counts[e].
 __global__ void __launch_bounds__(256)
 moe_rank_kernel(const int32_t* __restrict__ idx, int32_t* __restrict__ rank, int32_t* __restrict__ counts, int P) {
@@ -238,13 +344,67 @@ extern "C" int forge_moe_pair_gate_up(const void* x, const void* Wg, const void*
 extern "C" int forge_moe_pair_down(const void* act, const void* Wd, const int32_t* idx, const float* wts, float* y, int dtype, int T, int W,
                                    int F, int top, cudaStream_t stream) {
     if (T < 0 || W <= 0 || F <= 0 || top <= 0) return forge::fail(FORGE_ERR_ARG, "moe_pair_down: bad sizes T=%d W=%d F=%d top=%d", T, W, F, top);
-    if ((size_t)top * F * sizeof(float) > 48 * 1024) return forge::fail(FORGE_ERR_UNSUPPORTED, "moe_pair_down: %d experts of %d channels a token", top, F);
+    if ((size_t)top * F * sizeof(float) > 200 * 1024) return forge::fail(FORGE_ERR_UNSUPPORTED, "moe_pair_down: %d experts of %d channels a token", top, F);
     if (T == 0) return FORGE_OK;
     cudaError_t e = cudaSuccess;
+    static forge::PerDeviceFlag attr[2];
+    bool& done = attr[dtype == FORGE_BF16].current();
+    if (!done && (size_t)top * F * sizeof(float) > 48 * 1024) {
+        FORGE_DISPATCH_DTYPE(dtype, TT,
+            e = cudaFuncSetAttribute(moe_pair_down_kernel<TT, TT>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+        if (e != cudaSuccess) return forge::check_launch("moe_pair_down (shared memory)", e);
+        done = true;
+    }
     FORGE_DISPATCH_DTYPE(dtype, TT,
         e = forge::launch(moe_pair_down_kernel<TT, TT>, dim3(T, (W + kPairOutputs - 1) / kPairOutputs), dim3(128), sizeof(float) * top * F, stream,
                           1, (const TT*)act, (const TT*)Wd, idx, wts, y, W, F, top));
     return forge::check_launch("moe_pair_down", e);
+}
+
+namespace {
+constexpr size_t kExpertSmemLimit = 200 * 1024;
+forge::PerDeviceFlag g_expert_attr[4];
+
+// rows staged at a time for a reduction of K channels and P pairs, 0 if not even one fits
+int expert_rows_group(int K, int P) {
+    const size_t left = kExpertSmemLimit - std::min(kExpertSmemLimit, (size_t)P * sizeof(int));
+    return (int)std::min<size_t>(kGroupTokens, left / ((size_t)K * sizeof(float)));
+}
+
+template <typename TT, bool GATED>
+cudaError_t launch_expert_rows(int which, cudaStream_t stream, const void* in, int in_div, const void* Wa, const void* Wb, long long ld,
+                               long long expert_stride, const int32_t* idx, void* out, int P, int K, int N, int E) {
+    const int nt = expert_rows_group(K, P);
+    const size_t smem = (size_t)nt * K * sizeof(float) + (size_t)P * sizeof(int);
+    bool& done = g_expert_attr[which].current();
+    if (!done) {
+        cudaError_t e = cudaFuncSetAttribute(moe_expert_rows_kernel<TT, TT, GATED>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kExpertSmemLimit);
+        if (e != cudaSuccess) return e;
+        done = true;
+    }
+    return forge::launch(moe_expert_rows_kernel<TT, TT, GATED>, dim3(E, (N + kPairOutputs - 1) / kPairOutputs), dim3(128), smem, stream, 1,
+                         (const TT*)in, in_div, (const TT*)Wa, (const TT*)Wb, ld, expert_stride, idx, out, P, K, N, nt);
+}
+}  // namespace
+
+// 1 if the expert-by-expert path takes a step of P pairs with reductions of W and F channels.
+extern "C" int forge_moe_expert_supports(int P, int W, int F) { return (expert_rows_group(W, P) >= 1 && expert_rows_group(F, P) >= 1) ? 1 : 0; }
+
+// The path by pairs, expert by expert: act [P, F] of type dtype (scratch), ys fp32 [P, W] = W_down[e_p] act[p] (a later
+// moe_combine with dest[p] = p weighs and adds).  x [T, W]; Wg, Wu as in forge_moe_pair_gate_up; Wd [E, W, F]; idx int32 [P = T * top].
+extern "C" int forge_moe_expert_rows(const void* x, const void* Wg, const void* Wu, long long ld, const void* Wd, const int32_t* idx, void* act,
+                                     float* ys, int dtype, int T, int W, int F, int E, int top, cudaStream_t stream) {
+    if (T < 0 || W <= 0 || F <= 0 || E <= 0 || top <= 0) return forge::fail(FORGE_ERR_ARG, "moe_expert_rows: bad sizes T=%d W=%d F=%d E=%d top=%d", T, W, F, E, top);
+    const int P = T * top;
+    if (!forge_moe_expert_supports(P, W, F)) return forge::fail(FORGE_ERR_UNSUPPORTED, "moe_expert_rows: rows of %d and %d channels, %d pairs", W, F, P);
+    if (T == 0) return FORGE_OK;
+    cudaError_t e = cudaSuccess;
+    FORGE_DISPATCH_DTYPE(dtype, TT, {
+        e = launch_expert_rows<TT, true>(dtype == FORGE_BF16 ? 0 : 1, stream, x, top, Wg, Wu, ld, (long long)F * ld, idx, act, P, W, F, E);
+        if (e == cudaSuccess)
+            e = launch_expert_rows<TT, false>(dtype == FORGE_BF16 ? 2 : 3, stream, act, 1, Wd, nullptr, F, (long long)W * F, idx, ys, P, F, W, E);
+    });
+    return forge::check_launch("moe_expert_rows", e);
 }
 
 // idx int32 [P]; rank, dest int32 [P]; counts int32 [E]; x [T, W], xg [P, W] of type dtype.

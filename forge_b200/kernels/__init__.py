@@ -90,6 +90,8 @@ _SIGNATURES = {
         "forge_moe_route": [_P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _P],
         "forge_moe_pair_gate_up": [_P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _LL, _P],
         "forge_moe_pair_down": [_P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _P],
+        "forge_moe_expert_supports": [_I, _I, _I],
+        "forge_moe_expert_rows": [_P, _P, _P, _LL, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _P],
         "forge_moe_sort": [_P, _I, _P, _P, _P, _P, _P, _I, _I, _I, _I, _P],
         "forge_moe_combine": [_P, _P, _P, _P, _I, _I, _I, _P],
     },
@@ -1167,6 +1169,42 @@ def moe_pairs(x, idx, wts, w_gate_up, w_down):
                                         _need(wts, "wts", torch.float32), _need(y, "y"), dtype_code(x.dtype), T, W, F, top, _stream()),
            "moe_pair_down")
     return y
+
+
+def moe_experts_supported(P, W, F):
+    return bool(library("moe").forge_moe_expert_supports.fn(int(P), int(W), int(F)))
+
+
+def moe_experts(x, idx, wts, w_gate_up, w_down):
+    """The same as ``moe_pairs`` to the last bit, expert by expert: an expert's weight rows are read once for up to eight of the
+    pairs that chose it instead of once per pair.  Reads everything from device memory; three launches."""
+    lib = library("moe")
+    T, W = x.shape
+    E, F2, _ = w_gate_up.shape
+    F = F2 // 2
+    top = idx.shape[1]
+    act = new_tensor((T * top, F), x.dtype, x.device)
+    ys = new_tensor((T * top, W), torch.float32, x.device)
+    gp = _need(w_gate_up, "w_gate_up", x.dtype)
+    _check(lib, lib.forge_moe_expert_rows(_need(x, "x", ndim=2), gp, gp + W * x.element_size(), 2 * W, _need(w_down, "w_down", x.dtype),
+                                          _need(idx, "idx", torch.int32), _need(act, "act"), _need(ys, "ys"), dtype_code(x.dtype), T, W, F, E, top,
+                                          _stream()), "moe_expert_rows")
+    count_launches(1)
+    return moe_combine(ys, _pair_numbers(T, top, x.device), wts)
+
+
+_PAIR_NUMBERS = {}
+
+
+def _pair_numbers(T, top, device):
+    """int32 [T, top] = the pairs' own numbers (kept: a CUDA graph must not allocate it anew at every capture)."""
+    key = (T, top, str(device))
+    t = _PAIR_NUMBERS.get(key)
+    if t is None:
+        if len(_PAIR_NUMBERS) > 256:
+            _PAIR_NUMBERS.clear()
+        t = _PAIR_NUMBERS[key] = torch.arange(T * top, dtype=torch.int32, device=device).view(T, top)
+    return t
 
 
 def moe_sort(x, idx, E):

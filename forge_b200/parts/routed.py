@@ -4,7 +4,8 @@
     y = sum over the chosen e of s_e * Wdown_e (silu(Wgate_e x) * (Wup_e x))          (s_e divided by their sum with ``renormalize``)
 
 The router's arithmetic is fp32.  Steps of few tokens, and every step that a CUDA graph replays, take each (token, expert)
-pair on its own with everything read from device memory; steps of many tokens rank the pairs by expert, run every
+pair on its own with everything read from device memory (from two tokens on expert by expert, so that several pairs share one
+pass over an expert's weights; the numbers are the same to the last bit); steps of many tokens rank the pairs by expert, run every
 expert's rows through the ordinary matrix products, and add a token's experts up in the router's order.
 """
 import torch
@@ -19,6 +20,7 @@ from .linear import Linear
 class RoutedExperts(Part):
     graph_safe = True
     SORTED_FROM = 128          # tokens in a step from which the pairs are ranked by expert
+    BY_EXPERT_FROM = 2         # ... and from which the path by pairs goes expert by expert (the same numbers, fewer reads)
 
     def __init__(self, rt, hidden_size, intermediate_size, experts, top, score="sigmoid", renormalize=False, prefix="mlp."):
         if not 1 <= top <= experts:
@@ -71,6 +73,8 @@ class RoutedExperts(Part):
         idx, wts = kernels.moe_route(x, self.router, self.top, softmax=self.score == "softmax", renorm=self.renormalize)
         if x.shape[0] >= self.SORTED_FROM and not torch.cuda.is_current_stream_capturing():
             y = self._ranked(x, idx, wts)
+        elif x.shape[0] >= self.BY_EXPERT_FROM and kernels.moe_experts_supported(x.shape[0] * self.top, self.hidden_size, self.intermediate_size):
+            y = kernels.moe_experts(x, idx, wts, self.gate_up, self.down)
         else:
             y = kernels.moe_pairs(x, idx, wts, self.gate_up, self.down)
         if residual is None:
