@@ -49,7 +49,16 @@ struct GemmParams {
     const int32_t* slot_mapping;     // [M] page * page_size + offset of each row's token (negative or null: no cache write)
     __nv_bfloat16* kv_cache;         // [pages, 2, NKV, page_size, head_dim]
     int NH, NKV, head_dim, page_size;
+    // a device word that an earlier kernel wrote: where it holds 0 the whole product is skipped (nothing is read or written); null: none
+    const int* live;
 };
+
+// Every thread of every CTA leaves before anything is set up (no barrier, tensor memory or copy exists yet), all the same way.
+#define FORGE_SKIP_IF_NOT_LIVE(p)                       \
+    if ((p).live != nullptr) {                          \
+        forge::pdl_wait();                              \
+        if (*(p).live == 0) return;                     \
+    }
 
 template <int BN> struct Cfg {
     static constexpr int kStageBytes = (BM + BN) * BK * 2;
@@ -222,6 +231,7 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
                   const __grid_constant__ CUtensorMap tmap_c, const GemmParams p) {
     using C = Cfg<BN>;
     constexpr int kStages = C::kStages;
+    FORGE_SKIP_IF_NOT_LIVE(p);
     extern __shared__ uint8_t smem_raw[];
     // tiles need 1024-byte alignment for the 128-byte swizzle pattern to line up with the descriptors
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -495,6 +505,7 @@ gemm_sm100_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_
     constexpr int g = G > 0 ? G : 1;
     constexpr int kStages = C::kRingBlocks / g, BNH = PBN / 2;
     constexpr int kABytes = g * BM * BK * 2, kStageBytes = g * C::kBlockBytes;
+    FORGE_SKIP_IF_NOT_LIVE(p);
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     uint8_t* tiles = smem;                         // [kStages][ g tiles of A | g tiles of this CTA's half of W ]
@@ -734,6 +745,7 @@ gemm_sm100_splitk_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
     using C = SplitKCfg<G>;
     constexpr int kStages = C::kStages, BN = kSplitBN;
     constexpr int kTileA = BM * BK * 2, kTileW = BN * BK * 2;                            // one k-block of either operand
+    FORGE_SKIP_IF_NOT_LIVE(p);
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     uint8_t* tiles = smem;                                                               // slot: G tiles of A, then G tiles of W
@@ -988,6 +1000,7 @@ gemm_sm100_skinny_kernel(const __grid_constant__ CUtensorMap tmap_w, const __gri
     const int w_block = tile_rows * BK * 2;                                 // one k-block of the tile
     const int w_bytes = g * w_block, x_bytes = g * NT * BK * 2;           // one stage of each operand
     const int x_region = kStages * x_bytes;
+    FORGE_SKIP_IF_NOT_LIVE(p);
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     uint8_t* w_tiles = smem;                                   // [kStages][g][128 x 64]
@@ -1264,6 +1277,7 @@ __global__ void __launch_bounds__(kStreamKThreads, 1)
 gemm_sm100_streamk_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_x,
                           const GemmParams p, const StreamKWork wk, const int kStages) {
     using C = StreamKCfg<NT>;
+    FORGE_SKIP_IF_NOT_LIVE(p);
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     uint8_t* tiles = smem;
@@ -1764,8 +1778,7 @@ extern "C" int forge_gemm_sm100_set_workspace(void* ptr, long long bytes) {
 // the few-rows kernel with K cut across a cluster of that many CTAs; -100 (M <= 64 only) = the few-rows kernel
 // that deals units of work out evenly to persistent CTAs (the default once a workspace has been set).  status: device int, bit 1 raised if a wait ran out.
 extern "C" int forge_gemm_sm100(const void* A, const void* W, const float* bias, void* C, int* status, int M, int N,
-                                int K, int epilogue, int tile_n, void* reserved, cudaStream_t stream) {
-    (void)reserved;
+                                int K, int epilogue, int tile_n, const int* live, cudaStream_t stream) {
     if (M < 0 || N <= 0 || K <= 0) return forge::fail(FORGE_ERR_ARG, "gemm_sm100: bad sizes M=%d N=%d K=%d", M, N, K);
     if (M == 0) return FORGE_OK;
     if (K % 8 != 0) return forge::fail(FORGE_ERR_UNSUPPORTED, "gemm_sm100: K=%d is not a multiple of 8 (TMA row stride)", K);
@@ -1800,6 +1813,7 @@ extern "C" int forge_gemm_sm100(const void* A, const void* W, const float* bias,
             if (!bf16_tile_map(W, N, K, BM, &tw, &err)) return forge::fail(FORGE_ERR_UNSUPPORTED, "gemm_sm100: W: %s", err);
             if (!bf16_tile_map(A, M, K, nt, &tx, &err)) return forge::fail(FORGE_ERR_UNSUPPORTED, "gemm_sm100: A: %s", err);
             GemmParams p{C, bias, M, N, K, epilogue, status};
+            p.live = live;
             switch (nt) {
                 case 16: return launch_streamk<16>(tw, tx, p, stream);
                 case 32: return launch_streamk<32>(tw, tx, p, stream);
@@ -1851,6 +1865,7 @@ extern "C" int forge_gemm_sm100(const void* A, const void* W, const float* bias,
         // 128-wide tiles is the faster one there (22 against 28-33 us at [11264 x 2048])
         const bool token_major_instead = nt == 128 && tile_n == 0 && ksplit == 1;
         GemmParams p{C, bias, M, N, K, epilogue, status};
+        p.live = live;
         if (!token_major_instead) switch (nt) {
             case 16: return launch_skinny<16>(W, A, p, ksplit, tile_rows, stream);
             case 32: return launch_skinny<32>(W, A, p, ksplit, tile_rows, stream);
@@ -1873,6 +1888,7 @@ extern "C" int forge_gemm_sm100(const void* A, const void* W, const float* bias,
         }
         if (ks > 0) {
             GemmParams p{C, bias, M, N, K, epilogue, status};
+            p.live = live;
             return launch_splitk(A, W, p, ks, stream);
         }
     }
@@ -1909,6 +1925,7 @@ extern "C" int forge_gemm_sm100(const void* A, const void* W, const float* bias,
     if (bn == 512 || bn == 1192 || bn == 1128) {
         if (M <= BM) return forge::fail(FORGE_ERR_ARG, "gemm_sm100: the two-CTA tile is for more than %d rows, got %d", BM, M);
         GemmParams p{C, bias, M, N, K, epilogue, status};
+        p.live = live;
         if (bn == 512) return launch_pair(A, W, p, stream);
         if (K % BK != 0 || K < 2 * BK)
             return forge::fail(FORGE_ERR_UNSUPPORTED, "gemm_sm100: two-CTA tiles of %d columns need K %% 64 == 0 and K >= 128, got %d", bn - 1000, K);
@@ -1918,6 +1935,7 @@ extern "C" int forge_gemm_sm100(const void* A, const void* W, const float* bias,
     if (!bf16_tile_map(A, M, K, BM, &ta, &err)) return forge::fail(FORGE_ERR_UNSUPPORTED, "gemm_sm100: A: %s", err);
     if (!bf16_tile_map(W, N, K, bn, &tw, &err)) return forge::fail(FORGE_ERR_UNSUPPORTED, "gemm_sm100: W: %s", err);
     GemmParams p{C, bias, M, N, K, epilogue, status};
+    p.live = live;
     switch (bn) {
         case 256: return launch<256>(ta, tw, p, stream);
         case 224: return launch<224>(ta, tw, p, stream);

@@ -20,27 +20,51 @@ namespace {
 __device__ __forceinline__ float sigmoidf(float x) { return 1.0f / (1.0f + expf(-x)); }
 __device__ __forceinline__ float siluf(float x) { return x * sigmoidf(x); }
 
-// A warp per token.  scores in shared memory, [warp][E].
+// A CTA of 8 warps per token: the warps take the experts in turn (a lane sums its channels in order, 8 neighbours at a time
+// where the rows allow 16-byte loads, then the butterfly), thread 0 ranks the scores in shared memory [E].
 template <typename TA>
-__global__ void __launch_bounds__(128)
+__device__ __forceinline__ float route_dot(const TA* __restrict__ xr, const float* __restrict__ w, int W, int lane) {
+    float a = 0.f;
+    for (int c = lane; c < W; c += 32) a = fmaf(forge::to_float(xr[c]), w[c], a);
+    return a;
+}
+template <>
+__device__ __forceinline__ float route_dot<__nv_bfloat16>(const __nv_bfloat16* __restrict__ xr, const float* __restrict__ w, int W, int lane) {
+    float a = 0.f;
+    if ((W & 7) == 0 && (((uintptr_t)xr) & 15) == 0 && (((uintptr_t)w) & 15) == 0) {
+#pragma unroll 4
+        for (int c = lane * 8; c < W; c += 256) {
+            const uint4 raw = *reinterpret_cast<const uint4*>(xr + c);
+            const float4 w0 = *reinterpret_cast<const float4*>(w + c), w1 = *reinterpret_cast<const float4*>(w + c + 4);
+            const __nv_bfloat162* p = reinterpret_cast<const __nv_bfloat162*>(&raw);
+            const float2 x0 = __bfloat1622float2(p[0]), x1 = __bfloat1622float2(p[1]), x2 = __bfloat1622float2(p[2]), x3 = __bfloat1622float2(p[3]);
+            a = fmaf(x0.x, w0.x, a); a = fmaf(x0.y, w0.y, a); a = fmaf(x1.x, w0.z, a); a = fmaf(x1.y, w0.w, a);
+            a = fmaf(x2.x, w1.x, a); a = fmaf(x2.y, w1.y, a); a = fmaf(x3.x, w1.z, a); a = fmaf(x3.y, w1.w, a);
+        }
+        return a;
+    }
+    for (int c = lane; c < W; c += 32) a = fmaf(__bfloat162float(xr[c]), w[c], a);
+    return a;
+}
+
+constexpr int kRouteThreads = 256;
+
+template <typename TA>
+__global__ void __launch_bounds__(kRouteThreads)
 moe_route_kernel(const TA* __restrict__ x, const float* __restrict__ Wr, int32_t* __restrict__ idx, float* __restrict__ wts, int T,
                  int W, int E, int top, int softmax, int renorm) {
     extern __shared__ float sc[];
     forge::pdl_launch_dependents();
     forge::pdl_wait();
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, t = blockIdx.x * 4 + warp;
-    if (t >= T) return;
-    float* s = sc + warp * E;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, t = blockIdx.x;
+    float* s = sc;
     const TA* xr = x + (size_t)t * W;
-    for (int e = 0; e < E; ++e) {
-        const float* w = Wr + (size_t)e * W;
-        float a = 0.f;
-        for (int c = lane; c < W; c += 32) a = fmaf(forge::to_float(xr[c]), w[c], a);
-        a = forge::warp_sum(a);
+    for (int e = warp; e < E; e += kRouteThreads / 32) {
+        const float a = forge::warp_sum(route_dot(xr, Wr + (size_t)e * W, W, lane));
         if (lane == 0) s[e] = a;
     }
-    __syncwarp();
-    if (lane == 0) {
+    __syncthreads();
+    if (threadIdx.x == 0) {
         if (softmax) {
             float m = -INFINITY, sum = 0.f;
             for (int e = 0; e < E; ++e) m = fmaxf(m, s[e]);
@@ -92,54 +116,121 @@ __device__ __forceinline__ float lane_dot<__nv_bfloat16>(const __nv_bfloat16* __
     return a;
 }
 
-constexpr int kPairOutputs = 32;          // outputs per CTA (8 per warp)
+constexpr int kPairOutputs = 32;          // outputs per CTA of the expert-by-expert kernel (8 per warp)
+constexpr int kPairTile = 16;             // outputs per CTA of the kernels that take every pair on its own (4 per warp, all at once)
 
-// grid (pairs, ceil(F / 32)): act[pair, j] = act_fn(Wg[e][j] . x) * (Wu[e][j] . x);  row j of expert e lies at (e * F + j) * ld
+// R dot products at once, each summed exactly as lane_dot sums it, so that a lane has R 16-byte loads in flight instead of one:
+// rows w[r] against the vectors xs[r / XG] in shared memory (XG consecutive rows share a vector).
+template <typename TW, int R, int XG>
+__device__ __forceinline__ void lane_dot_rows(const TW* const (&w)[R], const float* const (&xs)[R / XG], int n, int lane, float (&a)[R]) {
+#pragma unroll
+    for (int r = 0; r < R; ++r) a[r] = 0.f;
+    bool vec = std::is_same<TW, __nv_bfloat16>::value && (n & 7) == 0;
+#pragma unroll
+    for (int r = 0; r < R; ++r) vec = vec && (((uintptr_t)w[r]) & 15) == 0;
+    if (vec) {
+        for (int c = lane * 8; c < n; c += 256) {
+            uint4 raw[R];
+#pragma unroll
+            for (int r = 0; r < R; ++r) raw[r] = *reinterpret_cast<const uint4*>(w[r] + c);
+#pragma unroll
+            for (int g = 0; g < R / XG; ++g) {
+                const float4 x0 = *reinterpret_cast<const float4*>(xs[g] + c), x1 = *reinterpret_cast<const float4*>(xs[g] + c + 4);
+                const float xv[8] = {x0.x, x0.y, x0.z, x0.w, x1.x, x1.y, x1.z, x1.w};
+#pragma unroll
+                for (int q = 0; q < XG; ++q) {
+                    const int r = g * XG + q;
+                    const __nv_bfloat162* p = reinterpret_cast<const __nv_bfloat162*>(&raw[r]);
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) {
+                        const float2 f = __bfloat1622float2(p[i]);
+                        a[r] = fmaf(f.x, xv[2 * i], a[r]);
+                        a[r] = fmaf(f.y, xv[2 * i + 1], a[r]);
+                    }
+                }
+            }
+        }
+        return;
+    }
+    for (int c = lane; c < n; c += 32) {
+#pragma unroll
+        for (int r = 0; r < R; ++r) a[r] = fmaf(forge::to_float(w[r][c]), xs[r / XG][c], a[r]);
+    }
+}
+
+// grid (pairs, ceil(F / 16)): act[pair, j] = act_fn(Wg[e][j] . x) * (Wu[e][j] . x);  row j of expert e lies at (e * F + j) * ld
 // in both (ld = W: two matrices [E, F, W]; ld = 2 W and Wu = Wg + W: one matrix whose rows alternate gate, up).
 template <typename TA, typename TW>
 __global__ void __launch_bounds__(128)
 moe_pair_gate_up_kernel(const TA* __restrict__ x, const TW* __restrict__ Wg, const TW* __restrict__ Wu, const int32_t* __restrict__ idx,
                         TA* __restrict__ act, int W, int F, int top, long long ld) {
-    extern __shared__ float xs[];
+    extern __shared__ __align__(16) float xs[];
     forge::pdl_launch_dependents();
     forge::pdl_wait();
     const int p = blockIdx.x, t = p / top, e = idx[p];
     for (int c = threadIdx.x; c < W; c += 128) xs[c] = forge::to_float(x[(size_t)t * W + c]);
     __syncthreads();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    for (int jj = 0; jj < kPairOutputs / 4; ++jj) {
-        const int j = blockIdx.y * kPairOutputs + warp * (kPairOutputs / 4) + jj;
-        if (j >= F) break;
-        const size_t row = ((size_t)e * F + j) * ld;
-        const float g = forge::warp_sum(lane_dot(Wg + row, xs, W, lane));
-        const float u = forge::warp_sum(lane_dot(Wu + row, xs, W, lane));
-        if (lane == 0) act[(size_t)p * F + j] = forge::from_float<TA>(siluf(g) * u);
+    const int j0 = blockIdx.y * kPairTile + warp * 4;
+    if (j0 >= F) return;
+    const TW* rows[8];
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+        const size_t row = ((size_t)e * F + min(j0 + q, F - 1)) * ld;      // beyond the last output: its row once more, not written
+        rows[2 * q] = Wg + row;
+        rows[2 * q + 1] = Wu + row;
+    }
+    const float* const xv[1] = {xs};
+    float a[8];
+    lane_dot_rows<TW, 8, 8>(rows, xv, W, lane, a);
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+        const float g = forge::warp_sum(a[2 * q]), u = forge::warp_sum(a[2 * q + 1]);
+        if (lane == 0 && j0 + q < F) act[(size_t)p * F + j0 + q] = forge::from_float<TA>(siluf(g) * u);
     }
 }
 
-// grid (T, ceil(Wd / 32)): y[t, n] = sum_k wts[t, k] * (Wd[e_k][n] . act[(t, k)]);  Wd [E, W, F].
+// grid (T, ceil(Wd / 16)): y[t, n] = sum_k wts[t, k] * (Wd[e_k][n] . act[(t, k)]);  Wd [E, W, F].
 template <typename TA, typename TW>
 __global__ void __launch_bounds__(128)
 moe_pair_down_kernel(const TA* __restrict__ act, const TW* __restrict__ Wd, const int32_t* __restrict__ idx, const float* __restrict__ wts,
                      float* __restrict__ y, int W, int F, int top) {
-    extern __shared__ float as[];             // [top][F]
+    extern __shared__ __align__(16) float as[];             // [top][F]
     forge::pdl_launch_dependents();
     forge::pdl_wait();
     const int t = blockIdx.x;
     for (int i = threadIdx.x; i < top * F; i += 128) as[i] = forge::to_float(act[(size_t)t * top * F + i]);
     __syncthreads();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    for (int nn = 0; nn < kPairOutputs / 4; ++nn) {
-        const int n = blockIdx.y * kPairOutputs + warp * (kPairOutputs / 4) + nn;
-        if (n >= W) break;
-        float sum = 0.f;
-        for (int k = 0; k < top; ++k) {
-            const int e = idx[(size_t)t * top + k];
-            const float d = forge::warp_sum(lane_dot(Wd + ((size_t)e * W + n) * F, as + k * F, F, lane));
-            sum = fmaf(wts[(size_t)t * top + k], d, sum);
+    const int n0 = blockIdx.y * kPairTile + warp * 4;
+    if (n0 >= W) return;
+    float sum[4] = {0.f, 0.f, 0.f, 0.f};
+    // two of the token's experts at a time (the last one alone if their number is odd), added in the router's order
+    for (int k = 0; k < top; k += 2) {
+        const int k1 = min(k + 1, top - 1);
+        const int e0 = idx[(size_t)t * top + k], e1 = idx[(size_t)t * top + k1];
+        const TW* rows[8];
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+            const int n = min(n0 + q, W - 1);
+            rows[q] = Wd + ((size_t)e0 * W + n) * F;
+            rows[4 + q] = Wd + ((size_t)e1 * W + n) * F;
         }
-        if (lane == 0) y[(size_t)t * W + n] = sum;
+        const float* const av[2] = {as + (size_t)k * F, as + (size_t)k1 * F};
+        float d[8];
+        lane_dot_rows<TW, 8, 4>(rows, av, F, lane, d);
+        const float w0 = wts[(size_t)t * top + k], w1 = wts[(size_t)t * top + k1];
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+            sum[q] = fmaf(w0, forge::warp_sum(d[q]), sum[q]);
+            const float second = forge::warp_sum(d[4 + q]);
+            if (k + 1 < top) sum[q] = fmaf(w1, second, sum[q]);
+        }
     }
+    if (lane == 0)
+#pragma unroll
+        for (int q = 0; q < 4; ++q)
+            if (n0 + q < W) y[(size_t)t * W + n0 + q] = sum[q];
 }
 
 constexpr int kGroupTokens = 8;           // input rows that share one pass over an expert's weight rows
@@ -276,19 +367,21 @@ moe_rank_kernel(const int32_t* __restrict__ idx, int32_t* __restrict__ rank, int
     if (threadIdx.x == 0) counts[e] = base;
 }
 
-// One CTA per pair: its row in the sorted order = (pairs of lower experts) + rank; copies the token's input there.
+// One CTA per pair: its row in the sorted order = (pairs of lower experts) + rank, or with room for `cap` rows per expert
+// (cap > 0) expert * cap + rank; copies the token's input there.
 template <typename TA>
 __global__ void __launch_bounds__(128)
 moe_gather_kernel(const TA* __restrict__ x, const int32_t* __restrict__ idx, const int32_t* __restrict__ rank,
-                  const int32_t* __restrict__ counts, int32_t* __restrict__ dest, TA* __restrict__ xg, int W, int top) {
+                  const int32_t* __restrict__ counts, int32_t* __restrict__ dest, TA* __restrict__ xg, int W, int top, int cap) {
     __shared__ int s_dest;
     forge::pdl_launch_dependents();
     forge::pdl_wait();
     const int p = blockIdx.x, t = p / top;
     if (threadIdx.x == 0) {
         const int e = idx[p];
-        int off = 0;
-        for (int i = 0; i < e; ++i) off += counts[i];
+        int off = e * cap;
+        if (cap <= 0)
+            for (int i = 0; i < e; ++i) off += counts[i];
         s_dest = off + rank[p];
         dest[p] = s_dest;
     }
@@ -322,7 +415,7 @@ extern "C" int forge_moe_route(const void* x, int dtype, const float* Wr, int32_
     if (T == 0) return FORGE_OK;
     cudaError_t e = cudaSuccess;
     FORGE_DISPATCH_DTYPE(dtype, TT,
-        e = forge::launch(moe_route_kernel<TT>, dim3((T + 3) / 4), dim3(128), sizeof(float) * 4 * E, stream, 1, (const TT*)x, Wr, idx, wts, T, W,
+        e = forge::launch(moe_route_kernel<TT>, dim3(T), dim3(kRouteThreads), sizeof(float) * E, stream, 1, (const TT*)x, Wr, idx, wts, T, W,
                           E, top, softmax, renorm));
     return forge::check_launch("moe_route", e);
 }
@@ -335,7 +428,7 @@ extern "C" int forge_moe_pair_gate_up(const void* x, const void* Wg, const void*
     if (T == 0) return FORGE_OK;
     cudaError_t e = cudaSuccess;
     FORGE_DISPATCH_DTYPE(dtype, TT,
-        e = forge::launch(moe_pair_gate_up_kernel<TT, TT>, dim3(T * top, (F + kPairOutputs - 1) / kPairOutputs), dim3(128), sizeof(float) * W,
+        e = forge::launch(moe_pair_gate_up_kernel<TT, TT>, dim3(T * top, (F + kPairTile - 1) / kPairTile), dim3(128), sizeof(float) * W,
                           stream, 1, (const TT*)x, (const TT*)Wg, (const TT*)Wu, idx, (TT*)act, W, F, top, ld));
     return forge::check_launch("moe_pair_gate_up", e);
 }
@@ -356,7 +449,7 @@ extern "C" int forge_moe_pair_down(const void* act, const void* Wd, const int32_
         done = true;
     }
     FORGE_DISPATCH_DTYPE(dtype, TT,
-        e = forge::launch(moe_pair_down_kernel<TT, TT>, dim3(T, (W + kPairOutputs - 1) / kPairOutputs), dim3(128), sizeof(float) * top * F, stream,
+        e = forge::launch(moe_pair_down_kernel<TT, TT>, dim3(T, (W + kPairTile - 1) / kPairTile), dim3(128), sizeof(float) * top * F, stream,
                           1, (const TT*)act, (const TT*)Wd, idx, wts, y, W, F, top));
     return forge::check_launch("moe_pair_down", e);
 }
@@ -407,15 +500,16 @@ extern "C" int forge_moe_expert_rows(const void* x, const void* Wg, const void* 
     return forge::check_launch("moe_expert_rows", e);
 }
 
-// idx int32 [P]; rank, dest int32 [P]; counts int32 [E]; x [T, W], xg [P, W] of type dtype.
+// idx int32 [P]; rank, dest int32 [P]; counts int32 [E]; x [T, W]; xg of type dtype: [P, W], or with cap > 0 [E * cap, W], expert e's
+// rows from row e * cap on (cap >= the most pairs one expert can get; the rows beyond an expert's count are not written).
 extern "C" int forge_moe_sort(const void* x, int dtype, const int32_t* idx, int32_t* rank, int32_t* counts, int32_t* dest, void* xg, int T,
-                              int W, int E, int top, cudaStream_t stream) {
+                              int W, int E, int top, int cap, cudaStream_t stream) {
     if (T < 0 || W <= 0 || E <= 0 || top <= 0) return forge::fail(FORGE_ERR_ARG, "moe_sort: bad sizes T=%d W=%d E=%d top=%d", T, W, E, top);
     if (T == 0) return FORGE_OK;
     cudaError_t e = forge::launch(moe_rank_kernel, dim3(E), dim3(256), 0, stream, 1, idx, rank, counts, T * top);
     if (e != cudaSuccess) return forge::check_launch("moe_sort (rank)", e);
     FORGE_DISPATCH_DTYPE(dtype, TT,
-        e = forge::launch(moe_gather_kernel<TT>, dim3(T * top), dim3(128), 0, stream, 1, (const TT*)x, idx, rank, counts, dest, (TT*)xg, W, top));
+        e = forge::launch(moe_gather_kernel<TT>, dim3(T * top), dim3(128), 0, stream, 1, (const TT*)x, idx, rank, counts, dest, (TT*)xg, W, top, cap));
     return forge::check_launch("moe_sort", e);
 }
 

@@ -92,7 +92,7 @@ _SIGNATURES = {
         "forge_moe_pair_down": [_P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _P],
         "forge_moe_expert_supports": [_I, _I, _I],
         "forge_moe_expert_rows": [_P, _P, _P, _LL, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _P],
-        "forge_moe_sort": [_P, _I, _P, _P, _P, _P, _P, _I, _I, _I, _I, _P],
+        "forge_moe_sort": [_P, _I, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _P],
         "forge_moe_combine": [_P, _P, _P, _P, _I, _I, _I, _P],
     },
     "decode_layers": {
@@ -1207,18 +1207,21 @@ def _pair_numbers(T, top, device):
     return t
 
 
-def moe_sort(x, idx, E):
+def moe_sort(x, idx, E, cap=0):
     """The (token, expert) pairs ranked by (expert, token): returns (xg [T*top, W]: each pair's input row at its rank, counts int32 [E],
-    dest int32 [T, top]: the rank of every pair)."""
+    dest int32 [T, top]: the rank of every pair).  With ``cap`` (at least T) every expert has room for ``cap`` rows: xg [E*cap, W], expert
+    e's rows from e*cap on, the rows beyond its count left as they were; nothing then depends on the counts' values on the host."""
     lib = library("moe")
     T, W = x.shape
     top = idx.shape[1]
     rank = new_tensor((T * top,), torch.int32, x.device)
     dest = new_tensor((T, top), torch.int32, x.device)
     counts = new_tensor((E,), torch.int32, x.device)
-    xg = new_tensor((T * top, W), x.dtype, x.device)
+    if cap and cap < T:
+        raise KernelError(f"moe_sort: room for {cap} rows per expert, a step of {T} tokens")
+    xg = new_tensor((E * cap if cap else T * top, W), x.dtype, x.device)
     _check(lib, lib.forge_moe_sort(_need(x, "x", ndim=2), dtype_code(x.dtype), _need(idx, "idx", torch.int32), _need(rank, "rank"),
-                                   _need(counts, "counts"), _need(dest, "dest"), _need(xg, "xg"), T, W, E, top, _stream()), "moe_sort")
+                                   _need(counts, "counts"), _need(dest, "dest"), _need(xg, "xg"), T, W, E, top, int(cap), _stream()), "moe_sort")
     count_launches(1)
     return xg, counts, dest
 
@@ -1639,11 +1642,13 @@ GELU_GATE_VARIANT = {"FORGE_GATE_GELU": 1}
 GELU_CAST_VARIANT = {"FORGE_CAST_ACT": 1}        # the library whose bfloat16 store applies the exact gelu first
 
 
-def gemm_sm100(x, w, bias=None, accumulate_into=None, epilogue="none", tile_n=0, status=None, out=None):
+def gemm_sm100(x, w, bias=None, accumulate_into=None, epilogue="none", tile_n=0, status=None, out=None, live=None):
     """bf16 x [M,K] . w [N,K]^T on the tcgen05 tensor cores, fp32 accumulation.
     epilogue "none": fp32 [M,N] (added into ``accumulate_into`` when given); "cast": bf16 [M,N];
     "swiglu": bf16 [M,N/2] = silu(y[:,2j]) * y[:,2j+1]; "geglu": the same with the tanh form of gelu; "gelu": bf16 [M,N] =
-    y/2 (1 + erf(y / sqrt 2))."""
+    y/2 (1 + erf(y / sqrt 2)).
+    ``live``: an int32 device word (a one-element tensor) written by an earlier kernel; where it holds 0 the product is skipped on the
+    device, nothing read and nothing written."""
     # the gelu gate lives in a variant of the library of its own, so that the silu epilogues stay as short as they were
     lib = library("gemm_sm100", GELU_GATE_VARIANT if epilogue == "geglu" else GELU_CAST_VARIANT if epilogue == "gelu" else None)
     (M, K), (N, K2) = x.shape, w.shape
@@ -1671,7 +1676,7 @@ def gemm_sm100(x, w, bias=None, accumulate_into=None, epilogue="none", tile_n=0,
     _gemm_workspace(lib, x.device)
     _check(lib, lib.forge_gemm_sm100(_need(x, "x", torch.bfloat16, 2), _need(w, "w", torch.bfloat16, 2),
                                      _opt(bias, "bias", torch.float32), _need(out, "out", want_dtype),
-                                     _need(status, "status", torch.int32), M, N, K, code, int(tile_n), None, _stream()),
+                                     _need(status, "status", torch.int32), M, N, K, code, int(tile_n), _opt(live, "live", torch.int32), _stream()),
            "gemm_sm100")
     return out
 

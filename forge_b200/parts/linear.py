@@ -23,7 +23,7 @@ class Linear:
     def replay_key(self):
         return ("linear", tuple(self.weight.shape), self.weight.dtype, self.bias is None, self.tensor_core)
 
-    def forward(self, x, accumulate_into=None, epilogue="none", out=None):
+    def forward(self, x, accumulate_into=None, epilogue="none", out=None, live=None):
         """x [M,K] in rt.dtype.
         epilogue "none":   fp32 [M,N] (added into ``accumulate_into`` if given, which is then returned)
         epilogue "swiglu": rt.dtype [M,N/2], out[:,j] = silu(y[:,2j]) * y[:,2j+1]
@@ -31,14 +31,17 @@ class Linear:
         epilogue "cast":   rt.dtype [M,N]
         epilogue "gelu" | "gelu_tanh" | "silu":  rt.dtype [M,N], the activation of every element
         ``out`` ("none", "swiglu", "geglu" only): the tensor the result is written into instead of a new one.
+        ``live`` (tensor-core products only): an int32 device word; where it holds 0 the product is skipped on the device.
         """
+        if live is not None and not self.tensor_core:
+            raise ValueError("a product that the device may skip is a tensor-core product")
         if epilogue == "gelu" and self.tensor_core:
             return kernels.gemm_sm100(x, self.weight, bias=self.bias, epilogue="gelu")      # the activation in the product's epilogue
         if epilogue in kernels.ACTIVATIONS:
             y = kernels.gemm_sm100(x, self.weight, bias=self.bias) if self.tensor_core else kernels.gemm_simt(x, self.weight, bias=self.bias)
             return kernels.act_rows(y, self.rt.dtype, epilogue)
         if self.tensor_core:
-            return kernels.gemm_sm100(x, self.weight, bias=self.bias, accumulate_into=accumulate_into, epilogue=epilogue, out=out)
+            return kernels.gemm_sm100(x, self.weight, bias=self.bias, accumulate_into=accumulate_into, epilogue=epilogue, out=out, live=live)
         if epilogue == "none":
             return kernels.gemm_simt(x, self.weight, bias=self.bias, out=out if accumulate_into is None else accumulate_into,
                                      accumulate=accumulate_into is not None)

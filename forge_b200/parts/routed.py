@@ -3,10 +3,16 @@
     s = sigmoid(Wr x)  (or softmax(Wr x));   the ``top`` largest s choose the experts (the lower index wins a tie)
     y = sum over the chosen e of s_e * Wdown_e (silu(Wgate_e x) * (Wup_e x))          (s_e divided by their sum with ``renormalize``)
 
-The router's arithmetic is fp32.  Steps of few tokens, and every step that a CUDA graph replays, take each (token, expert)
-pair on its own with everything read from device memory (from two tokens on expert by expert, so that several pairs share one
-pass over an expert's weights; the numbers are the same to the last bit); steps of many tokens rank the pairs by expert, run every
-expert's rows through the ordinary matrix products, and add a token's experts up in the router's order.
+The router's arithmetic is fp32.  Three paths, all with everything but the last one's row counts read from device memory:
+
+  by pairs      fewer (token, expert) pairs than experts: each pair on its own streams its expert's rows once (32-bit runs: every
+                step below the last path's size, from two tokens on expert by expert with the same numbers to the last bit)
+  with room     16-bit steps of up to 127 tokens, and every larger step that a CUDA graph replays: the pairs are ranked by expert into
+                a buffer with room for a step's tokens per expert (an expert is chosen at most once per token), every expert's rows go
+                through the tensor-core products, and a product whose expert nobody chose is skipped on the device by its row count
+  ranked        steps of many tokens: the pairs lie packed by expert, the row counts come to the host (one wait per layer) and
+                every expert's rows go through the ordinary matrix products
+A token's experts are added up in the router's order in all three.
 """
 import torch
 
@@ -68,11 +74,34 @@ class RoutedExperts(Part):
                 off += n
         return kernels.moe_combine(ys, dest, wts)
 
+    def _with_room(self, x, idx, wts):
+        """Nothing waits for the device: expert e's rows lie from row e * T on, and its two products are skipped where counts[e] is 0.
+        The rows beyond an expert's count hold whatever the buffer held; a product's rows do not mix, and nobody reads theirs."""
+        T, W, F, E = x.shape[0], self.hidden_size, self.intermediate_size, self.experts
+        xg, counts, dest = kernels.moe_sort(x, idx, E, cap=T)
+        act = kernels.new_tensor((E * T, F), self.rt.dtype, x.device)
+        ys = kernels.new_tensor((E * T, W), torch.float32, x.device)
+        for e in range(E):
+            rows, live = slice(e * T, (e + 1) * T), counts[e:e + 1]
+            self.gate_up_of[e].forward(xg[rows], epilogue="swiglu", out=act[rows], live=live)
+            self.down_of[e].forward(act[rows], out=ys[rows], live=live)
+        return kernels.moe_combine(ys, dest, wts)
+
+    def _pairs_fit(self):
+        """Whether the path by pairs holds a token's input and its experts' activations in a CTA's shared memory."""
+        return self.hidden_size <= 12000 and self.top * self.intermediate_size * 4 <= 200 * 1024
+
     def forward(self, x, residual):
         """Adds the output into ``residual`` fp32 [T, W], or (``residual`` None) returns it as a new fp32 [T, W]."""
         idx, wts = kernels.moe_route(x, self.router, self.top, softmax=self.score == "softmax", renorm=self.renormalize)
-        if x.shape[0] >= self.SORTED_FROM and not torch.cuda.is_current_stream_capturing():
+        T = x.shape[0]
+        tensor_core = self.gate_up_of[0].tensor_core and self.down_of[0].tensor_core
+        if T >= self.SORTED_FROM and not torch.cuda.is_current_stream_capturing():
             y = self._ranked(x, idx, wts)
+        elif tensor_core and (T * self.top >= self.experts or T >= self.SORTED_FROM or not self._pairs_fit()):
+            y = self._with_room(x, idx, wts)
+        elif tensor_core:
+            y = kernels.moe_pairs(x, idx, wts, self.gate_up, self.down)
         elif x.shape[0] >= self.BY_EXPERT_FROM and kernels.moe_experts_supported(x.shape[0] * self.top, self.hidden_size, self.intermediate_size):
             y = kernels.moe_experts(x, idx, wts, self.gate_up, self.down)
         else:
