@@ -19,6 +19,7 @@
 // alone, not on the step's cut, the tile, or the batch around it.
 #include "common.cuh"
 #include "checks.cuh"
+#include "mma_sync.cuh"
 
 namespace {
 
@@ -106,6 +107,123 @@ head_linear_kernel(const TI* __restrict__ in, long long in_ld, int in_hs, const 
             TO* dst = out + (size_t)(t0 + tt) * out_ld + (size_t)h * out_hs + N;
             dst[2 * p] = forge::from_float<TO>(u * cs - v * sn);
             dst[2 * p + 1] = forge::from_float<TO>(v * cs + u * sn);
+        }
+    }
+}
+
+// The same per-head product on the tensor cores for 16-bit weights: one CTA of four warps per (64 tokens, head, 64 output
+// channels), a warp 16 tokens.  The reduction runs over chunks of 128 input channels (all of a chunk's loads in flight at once); a chunk of the inputs (rounded to bfloat16
+// where they come as fp32) and of W_h is staged in shared memory, rows padded by 16 bytes so that the 8 x 8 matrix loads do not
+// meet in a bank, and multiplied by m16n8k16 products with fp32 sums.  Rows and channels beyond T, K and N are staged as
+// zeros.  The rotated channels are taken by the CTAs of the first channel tile, as in the kernel above.
+constexpr int kHlmThreads = 128, kHlmTile = 64, kHlmRow = kHlmTile + 8, kHlmK = 128, kHlmRowK = kHlmK + 8;
+
+template <typename TI>
+__device__ __forceinline__ uint4 load8_bf16(const TI* __restrict__ p, int valid, bool vec);
+template <>
+__device__ __forceinline__ uint4 load8_bf16<float>(const float* __restrict__ p, int valid, bool vec) {
+    float f[8];
+    if (vec && valid >= 8) {
+        const float4 a = *reinterpret_cast<const float4*>(p), b = *reinterpret_cast<const float4*>(p + 4);
+        f[0] = a.x; f[1] = a.y; f[2] = a.z; f[3] = a.w; f[4] = b.x; f[5] = b.y; f[6] = b.z; f[7] = b.w;
+    } else {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) f[i] = i < valid ? p[i] : 0.f;
+    }
+    return make_uint4(mma_sync::pack_bf16(f[0], f[1]), mma_sync::pack_bf16(f[2], f[3]), mma_sync::pack_bf16(f[4], f[5]), mma_sync::pack_bf16(f[6], f[7]));
+}
+template <>
+__device__ __forceinline__ uint4 load8_bf16<__nv_bfloat16>(const __nv_bfloat16* __restrict__ p, int valid, bool vec) {
+    if (vec && valid >= 8) return *reinterpret_cast<const uint4*>(p);
+    __align__(16) __nv_bfloat16 h[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) h[i] = i < valid ? p[i] : __float2bfloat16(0.f);
+    return *reinterpret_cast<const uint4*>(h);
+}
+
+template <typename TI>
+__global__ void __launch_bounds__(kHlmThreads)
+head_linear_mma_kernel(const TI* __restrict__ in, long long in_ld, int in_hs, const __nv_bfloat16* __restrict__ W, __nv_bfloat16* __restrict__ out,
+                       long long out_ld, int out_hs, const int32_t* __restrict__ positions, const float* __restrict__ freq, float amp,
+                       int T, int K, int N, int R) {
+    __shared__ __align__(16) __nv_bfloat16 As[kHlmTile][kHlmRowK];         // [token][input channel of the chunk]
+    __shared__ __align__(16) __nv_bfloat16 Bs[kHlmK][kHlmRow];             // [input channel of the chunk][output channel]
+    forge::pdl_launch_dependents();
+    forge::pdl_wait();
+    const int t0 = blockIdx.x * kHlmTile, h = blockIdx.y, n0 = blockIdx.z * kHlmTile;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    constexpr int kIn = 16 / (int)sizeof(TI);                              // input elements per 16 bytes
+    const bool a_vec = (in_ld % kIn) == 0 && (in_hs % kIn) == 0 && (reinterpret_cast<uintptr_t>(in) & 15) == 0;
+    const bool b_vec = (N & 7) == 0 && (reinterpret_cast<uintptr_t>(W) & 15) == 0;
+    const __nv_bfloat16* Wh = W + (size_t)h * K * N;
+    const int nt = min(kHlmTile, T - t0);
+    const bool warp_live = warp * 16 < nt;                                 // a warp whose 16 tokens lie beyond the step's has no sums
+    float acc[8][4];
+#pragma unroll
+    for (int i = 0; i < 8; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) acc[i][j] = 0.f;
+    constexpr int kPer = kHlmTile * kHlmK / 8 / kHlmThreads;               // 16-byte pieces per thread of each operand's chunk
+    for (int k0 = 0; k0 < K; k0 += kHlmK) {
+        uint4 av[kPer], bv[kPer];
+#pragma unroll
+        for (int j = 0; j < kPer; ++j) {
+            const int i = threadIdx.x + j * kHlmThreads;
+            const int ra = i / (kHlmK / 8), ca = (i % (kHlmK / 8)) * 8;    // a token's piece of 8 input channels
+            const int t = t0 + ra, k = k0 + ca;
+            av[j] = make_uint4(0u, 0u, 0u, 0u);
+            if (t < T && k < K) av[j] = load8_bf16<TI>(in + (size_t)t * in_ld + (size_t)h * in_hs + k, K - k, a_vec && (k % kIn) == 0);
+            const int rb = i / (kHlmTile / 8), cb = (i % (kHlmTile / 8)) * 8;   // an input channel's piece of 8 output channels
+            const int kb = k0 + rb, n = n0 + cb;
+            bv[j] = make_uint4(0u, 0u, 0u, 0u);
+            if (kb < K && n < N) bv[j] = load8_bf16<__nv_bfloat16>(Wh + (size_t)kb * N + n, N - n, b_vec);
+        }
+        __syncthreads();                                                   // the chunk before is read
+#pragma unroll
+        for (int j = 0; j < kPer; ++j) {
+            const int i = threadIdx.x + j * kHlmThreads;
+            *reinterpret_cast<uint4*>(&As[i / (kHlmK / 8)][(i % (kHlmK / 8)) * 8]) = av[j];
+            *reinterpret_cast<uint4*>(&Bs[i / (kHlmTile / 8)][(i % (kHlmTile / 8)) * 8]) = bv[j];
+        }
+        __syncthreads();
+        if (!warp_live) continue;
+        const int ksteps = min(kHlmK, K - k0 + 15) / 16;                   // the chunk's k-steps that hold channels
+        for (int ks = 0; ks < ksteps; ++ks) {
+            uint32_t a[4];
+            mma_sync::ldmatrix_x4(a, &As[warp * 16 + (lane & 15)][ks * 16 + (lane >> 4) * 8]);
+#pragma unroll
+            for (int np = 0; np < 4; ++np) {
+                uint32_t b[4];
+                mma_sync::ldmatrix_x4_trans(b, &Bs[ks * 16 + (lane & 7) + ((lane >> 3) & 1) * 8][np * 16 + (lane >> 4) * 8]);
+                mma_sync::mma_bf16(acc[2 * np], a, b[0], b[1]);
+                mma_sync::mma_bf16(acc[2 * np + 1], a, b[2], b[3]);
+            }
+        }
+    }
+#pragma unroll
+    for (int nb = 0; nb < 8; ++nb) {
+        const int n = n0 + nb * 8 + (lane & 3) * 2;
+#pragma unroll
+        for (int half = 0; half < 2; ++half) {
+            const int t = t0 + warp * 16 + (lane >> 2) + half * 8;
+            if (t >= T) continue;
+            __nv_bfloat16* dst = out + (size_t)t * out_ld + (size_t)h * out_hs + n;
+            if (n < N) dst[0] = __float2bfloat16(acc[nb][2 * half]);
+            if (n + 1 < N) dst[1] = __float2bfloat16(acc[nb][2 * half + 1]);
+        }
+    }
+    if (R > 0 && blockIdx.z == 0) {
+        for (int i = threadIdx.x; i < nt * (R >> 1); i += kHlmThreads) {
+            const int tt = i / (R >> 1), p = i % (R >> 1);
+            const TI* src = in + (size_t)(t0 + tt) * in_ld + (size_t)h * in_hs + K;
+            float sn, cs;
+            sincosf((float)positions[t0 + tt] * freq[p], &sn, &cs);
+            sn *= amp;
+            cs *= amp;
+            const float u = forge::to_float(src[2 * p]), v = forge::to_float(src[2 * p + 1]);
+            __nv_bfloat16* dst = out + (size_t)(t0 + tt) * out_ld + (size_t)h * out_hs + N;
+            dst[2 * p] = __float2bfloat16(u * cs - v * sn);
+            dst[2 * p + 1] = __float2bfloat16(v * cs + u * sn);
         }
     }
 }
@@ -247,15 +365,26 @@ extern "C" int forge_latent_prepare(const float* proj, int ld, const int32_t* po
 }
 
 // out[t, h, 0:N] = sum_k in[t, h, k] W[h, k, n], and (R > 0) out[t, h, N:N+R] = in[t, h, K:K+R] rotated by positions[t].
-// in of in_dtype (fp32 or bf16), W and out of dtype; leading dimensions and head strides in elements.
+// in of in_dtype (fp32 or bf16), W and out of dtype; leading dimensions and head strides in elements.  bf16 weights go to the
+// tensor cores (fp32 inputs rounded to bfloat16 on the way) unless `simt` asks for the fp32 multiply-adds.
 extern "C" int forge_head_linear(const void* in, int in_dtype, long long in_ld, int in_hs, const void* W, void* out, int dtype,
                                  long long out_ld, int out_hs, const int32_t* positions, const float* freq, float amp, int T, int H,
-                                 int K, int N, int R, cudaStream_t stream) {
+                                 int K, int N, int R, int simt, cudaStream_t stream) {
     if (T < 0 || H <= 0 || K <= 0 || N <= 0 || R < 0 || (R & 1)) return forge::fail(FORGE_ERR_ARG, "head_linear: bad sizes T=%d H=%d K=%d N=%d R=%d", T, H, K, N, R);
     if (R > 0 && (!positions || !freq)) return forge::fail(FORGE_ERR_ARG, "head_linear: a rotation needs positions and frequencies");
-    if (sizeof(float) * kLinTokens * K > 48 * 1024) return forge::fail(FORGE_ERR_UNSUPPORTED, "head_linear: %d input channels a head", K);
     if (T == 0) return FORGE_OK;
     cudaError_t e;
+    if (dtype == FORGE_BF16 && (in_dtype == FORGE_F32 || in_dtype == FORGE_BF16) && !simt) {
+        const dim3 grid((T + kHlmTile - 1) / kHlmTile, H, (N + kHlmTile - 1) / kHlmTile);
+        if (in_dtype == FORGE_F32)
+            e = forge::launch(head_linear_mma_kernel<float>, grid, dim3(kHlmThreads), 0, stream, 1, (const float*)in, in_ld, in_hs,
+                              (const __nv_bfloat16*)W, (__nv_bfloat16*)out, out_ld, out_hs, positions, freq, amp, T, K, N, R);
+        else
+            e = forge::launch(head_linear_mma_kernel<__nv_bfloat16>, grid, dim3(kHlmThreads), 0, stream, 1, (const __nv_bfloat16*)in, in_ld, in_hs,
+                              (const __nv_bfloat16*)W, (__nv_bfloat16*)out, out_ld, out_hs, positions, freq, amp, T, K, N, R);
+        return forge::check_launch("head_linear (tensor cores)", e);
+    }
+    if (sizeof(float) * kLinTokens * K > 48 * 1024) return forge::fail(FORGE_ERR_UNSUPPORTED, "head_linear: %d input channels a head", K);
     if (dtype == FORGE_F32 && in_dtype == FORGE_F32)
         e = launch_head_linear<float, float, float>(stream, in, in_ld, in_hs, W, out, out_ld, out_hs, positions, freq, amp, T, H, K, N, R);
     else if (dtype == FORGE_BF16 && in_dtype == FORGE_F32)

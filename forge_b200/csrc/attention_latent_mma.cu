@@ -279,12 +279,22 @@ latent_combine_kernel(const float* __restrict__ u, const float* __restrict__ par
         }
     }
     const float inv = l > 0.f ? 1.0f / l : 0.f;
-    for (int c = lane; c < C; c += 32) {
-        float a = 0.f;
+    // four channels a load (C is a multiple of 16), all runs' loads of a channel group in flight together
+    for (int c = lane * 4; c < C; c += 128) {
+        float4 part[kMaxSplit];
 #pragma unroll
         for (int s = 0; s < kMaxSplit; ++s)
-            if (s < nsplit && wt[s] != 0.f) a = fmaf(wt[s], u[((size_t)s * rows + w) * C + c], a);
-        out[(size_t)w * C + c] = __float2bfloat16_rn(a * inv);
+            if (s < nsplit && wt[s] != 0.f) part[s] = *reinterpret_cast<const float4*>(u + ((size_t)s * rows + w) * C + c);
+        float4 a = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+        for (int s = 0; s < kMaxSplit; ++s)
+            if (s < nsplit && wt[s] != 0.f) {
+                a.x = fmaf(wt[s], part[s].x, a.x); a.y = fmaf(wt[s], part[s].y, a.y);
+                a.z = fmaf(wt[s], part[s].z, a.z); a.w = fmaf(wt[s], part[s].w, a.w);
+            }
+        __nv_bfloat162* o = reinterpret_cast<__nv_bfloat162*>(out + (size_t)w * C + c);
+        o[0] = __floats2bfloat162_rn(a.x * inv, a.y * inv);
+        o[1] = __floats2bfloat162_rn(a.z * inv, a.w * inv);
     }
 }
 

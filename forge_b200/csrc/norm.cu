@@ -162,6 +162,46 @@ rmsnorm_add_kernel(const float* __restrict__ y, const float* __restrict__ w_y, f
     forge::pdl_wait();
     const float* yr = y + (size_t)blockIdx.x * H;
     float* rr = r + (size_t)blockIdx.x * H;
+    TOut* o = out + (size_t)blockIdx.x * H;
+    // rows of a multiple of four channels on 16-byte boundaries go four channels a load, eight loads in flight per thread (a step of
+    // one token is one CTA: what it waits for is the memory's latency, once per load that depends on another)
+    if ((H & 3) == 0 && (((uintptr_t)y | (uintptr_t)r | (uintptr_t)w_y | (uintptr_t)w_next) & 15) == 0) {
+        const int H4 = H >> 2;
+        const float4* y4 = reinterpret_cast<const float4*>(yr);
+        float4* r4 = reinterpret_cast<float4*>(rr);
+        const float4* wy4 = reinterpret_cast<const float4*>(w_y);
+        const float4* wn4 = reinterpret_cast<const float4*>(w_next);
+        float ss = 0.f;
+#pragma unroll 8
+        for (int c = threadIdx.x; c < H4; c += kNormThreads) {
+            const float4 v = y4[c];
+            ss = fmaf(v.x, v.x, ss); ss = fmaf(v.y, v.y, ss); ss = fmaf(v.z, v.z, ss); ss = fmaf(v.w, v.w, ss);
+        }
+        ss = forge::block_sum(ss, red);
+        const float inv = 1.0f / sqrtf(ss / (float)H + eps);
+        float s2 = 0.f;
+#pragma unroll 8
+        for (int c = threadIdx.x; c < H4; c += kNormThreads) {
+            const float4 a = y4[c], w = wy4[c];
+            float4 v = r4[c];
+            v.x = fmaf(mult, a.x * inv * w.x, v.x); v.y = fmaf(mult, a.y * inv * w.y, v.y);
+            v.z = fmaf(mult, a.z * inv * w.z, v.z); v.w = fmaf(mult, a.w * inv * w.w, v.w);
+            r4[c] = v;
+            s2 = fmaf(v.x, v.x, s2); s2 = fmaf(v.y, v.y, s2); s2 = fmaf(v.z, v.z, s2); s2 = fmaf(v.w, v.w, s2);
+        }
+        if (w_next == nullptr) return;
+        s2 = forge::block_sum(s2, red);
+        const float inv2 = 1.0f / sqrtf(s2 / (float)H + eps);
+#pragma unroll 8
+        for (int c = threadIdx.x; c < H4; c += kNormThreads) {
+            const float4 v = r4[c], w = wn4[c];
+            o[4 * c] = forge::from_float<TOut>(v.x * inv2 * w.x);
+            o[4 * c + 1] = forge::from_float<TOut>(v.y * inv2 * w.y);
+            o[4 * c + 2] = forge::from_float<TOut>(v.z * inv2 * w.z);
+            o[4 * c + 3] = forge::from_float<TOut>(v.w * inv2 * w.w);
+        }
+        return;
+    }
     float ss = 0.f;
     for (int c = threadIdx.x; c < H; c += kNormThreads) ss = fmaf(yr[c], yr[c], ss);
     ss = forge::block_sum(ss, red);
@@ -175,7 +215,6 @@ rmsnorm_add_kernel(const float* __restrict__ y, const float* __restrict__ w_y, f
     if (w_next == nullptr) return;
     s2 = forge::block_sum(s2, red);
     const float inv2 = 1.0f / sqrtf(s2 / (float)H + eps);
-    TOut* o = out + (size_t)blockIdx.x * H;
     for (int c = threadIdx.x; c < H; c += kNormThreads) o[c] = forge::from_float<TOut>(rr[c] * inv2 * w_next[c]);
 }
 

@@ -80,7 +80,7 @@ _SIGNATURES = {
     },
     "latent": {
         "forge_latent_prepare": [_P, _I, _P, _P, _P, _F, _P, _P, _P, _P, _I, _I, _I, _I, _I, _F, _P],
-        "forge_head_linear": [_P, _I, _LL, _I, _P, _P, _I, _LL, _I, _P, _P, _F, _I, _I, _I, _I, _I, _P],
+        "forge_head_linear": [_P, _I, _LL, _I, _P, _P, _I, _LL, _I, _P, _P, _F, _I, _I, _I, _I, _I, _I, _P],
         "forge_latent_attention": [_P] * 8 + [_I] * 8 + [_F, _I, _I, _P],
         "forge_latent_mma_supports": [_I] * 4,
         "forge_latent_mma_heads": [_I],
@@ -1062,10 +1062,11 @@ def latent_prepare(proj, batch, slot_mapping, cache, freq, amp, wq, wc, Cq, C, R
     return cq
 
 
-def head_linear(x, w, H, K, N, out_dtype, R=0, positions=None, freq=None, amp=1.0):
+def head_linear(x, w, H, K, N, out_dtype, R=0, positions=None, freq=None, amp=1.0, simt=False):
     """out[t, h, :N] = sum_k x[t, h, k] w[h, k, :] for the H heads of x [T, H*(K+R)] (fp32 or the weights' type); with R > 0 a head's
     last R channels are rotated by position * freq (channel 2i with 2i+1, cos and sin times ``amp``) and follow the N outputs.
-    w [H, K, N] in ``out_dtype``; returns [T, H*(N+R)] in ``out_dtype``."""
+    w [H, K, N] in ``out_dtype``; returns [T, H*(N+R)] in ``out_dtype``.  bfloat16 weights go to the tensor cores (an fp32 x rounded to
+    bfloat16 on the way) unless ``simt`` asks for fp32 multiply-adds on the inputs as they are."""
     lib = library("latent")
     T = x.shape[0]
     if x.shape[1] != H * (K + R) or tuple(w.shape) != (H, K, N) or w.dtype != out_dtype:
@@ -1074,7 +1075,7 @@ def head_linear(x, w, H, K, N, out_dtype, R=0, positions=None, freq=None, amp=1.
     _check(lib, lib.forge_head_linear(
         _need(x, "x", ndim=2), dtype_code(x.dtype), H * (K + R), K + R, _need(w, "w"), _need(out, "out", out_dtype), dtype_code(out_dtype),
         H * (N + R), N + R, _opt(positions, "positions", torch.int32), _opt(freq, "freq", torch.float32), float(amp), T, H, K, N, R,
-        _stream()), "head_linear")
+        1 if simt else 0, _stream()), "head_linear")
     return out
 
 

@@ -162,6 +162,30 @@ def test_retention_positions_count_from_the_request_start(dtype):
     assert max_rel_err(got["a"], want) <= PART_TOL[dtype] and max_rel_err(got["b"], want) <= PART_TOL[dtype]
 
 
+# ----------------------------------------------------------------------------------------------- the products per head
+
+@pytest.mark.parametrize("in_dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("T, H, K, N, R", [(1, 3, 8, 20, 4), (150, 2, 72, 70, 6), (67, 5, 128, 64, 0), (9, 1, 200, 129, 2), (130, 4, 64, 136, 8)])
+def test_products_per_head_on_the_tensor_cores(in_dtype, T, H, K, N, R):
+    """Token, channel and reduction counts that do not fill the kernel's tiles of 64; the rotated channels behind the outputs."""
+    from forge_b200 import kernels
+    x = rand(T, H * (K + R), seed=T + K).to(in_dtype)
+    w = rand(H, K, N, seed=N, scale=0.2).to(torch.bfloat16)
+    pos = torch.arange(5, 5 + T, dtype=torch.int32)
+    freq = torch.tensor([0.5 ** i for i in range(R // 2)], dtype=torch.float32)
+    args = dict(R=R, positions=pos.to(DEV), freq=freq.to(DEV), amp=1.25) if R else {}
+    got = kernels.head_linear(x.to(DEV), w.to(DEV), H, K, N, torch.bfloat16, **args).float().cpu().view(T, H, N + R)
+    simt = kernels.head_linear(x.to(DEV), w.to(DEV), H, K, N, torch.bfloat16, simt=True, **args).float().cpu().view(T, H, N + R)
+    xd = x.double().view(T, H, K + R)
+    want = torch.einsum("thk,hkn->thn", xd[..., :K].to(torch.bfloat16).double(), w.double())
+    assert max_rel_err(got[..., :N], want) <= 6e-3 and max_rel_err(simt[..., :N], want) <= 8e-3
+    if R:
+        a = pos.double()[:, None] * freq.double()[None, :]
+        u, v = xd[..., K::2], xd[..., K + 1::2]
+        rot = torch.stack([u * a.cos()[:, None] - v * a.sin()[:, None], v * a.cos()[:, None] + u * a.sin()[:, None]], dim=-1).flatten(-2) * 1.25
+        assert max_rel_err(got[..., N:], rot) <= 6e-3 and max_rel_err(simt[..., N:], rot) <= 6e-3
+
+
 # ----------------------------------------------------------------------------------------------- latent attention
 
 STRETCH = {"factor": 4.0, "original": 64, "fast": 8.0, "slow": 2.0}
