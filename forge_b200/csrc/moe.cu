@@ -121,7 +121,7 @@ constexpr int kPairTile = 16;             // outputs per CTA of the kernels that
 
 // R dot products at once, each summed exactly as lane_dot sums it, so that a lane has R 16-byte loads in flight instead of one:
 // rows w[r] against the vectors xs[r / XG] in shared memory (XG consecutive rows share a vector).
-template <typename TW, int R, int XG>
+template <typename TW, int R, int XG, int DEEP = 1>
 __device__ __forceinline__ void lane_dot_rows(const TW* const (&w)[R], const float* const (&xs)[R / XG], int n, int lane, float (&a)[R]) {
 #pragma unroll
     for (int r = 0; r < R; ++r) a[r] = 0.f;
@@ -129,23 +129,33 @@ __device__ __forceinline__ void lane_dot_rows(const TW* const (&w)[R], const flo
 #pragma unroll
     for (int r = 0; r < R; ++r) vec = vec && (((uintptr_t)w[r]) & 15) == 0;
     if (vec) {
-        for (int c = lane * 8; c < n; c += 256) {
-            uint4 raw[R];
+        // DEEP pieces of every row are asked for before the first is used (where few CTAs fit an SM, more bytes have to be in
+        // flight per lane); a row's pieces are added in the order of their channels all the same
+        for (int c0 = lane * 8; c0 < n; c0 += 256 * DEEP) {
+            uint4 raw[DEEP][R];
 #pragma unroll
-            for (int r = 0; r < R; ++r) raw[r] = *reinterpret_cast<const uint4*>(w[r] + c);
+            for (int d = 0; d < DEEP; ++d)
 #pragma unroll
-            for (int g = 0; g < R / XG; ++g) {
-                const float4 x0 = *reinterpret_cast<const float4*>(xs[g] + c), x1 = *reinterpret_cast<const float4*>(xs[g] + c + 4);
-                const float xv[8] = {x0.x, x0.y, x0.z, x0.w, x1.x, x1.y, x1.z, x1.w};
+                for (int r = 0; r < R; ++r)
+                    if (c0 + d * 256 < n) raw[d][r] = *reinterpret_cast<const uint4*>(w[r] + c0 + d * 256);
 #pragma unroll
-                for (int q = 0; q < XG; ++q) {
-                    const int r = g * XG + q;
-                    const __nv_bfloat162* p = reinterpret_cast<const __nv_bfloat162*>(&raw[r]);
+            for (int d = 0; d < DEEP; ++d) {
+                const int c = c0 + d * 256;
+                if (c >= n) break;
 #pragma unroll
-                    for (int i = 0; i < 4; ++i) {
-                        const float2 f = __bfloat1622float2(p[i]);
-                        a[r] = fmaf(f.x, xv[2 * i], a[r]);
-                        a[r] = fmaf(f.y, xv[2 * i + 1], a[r]);
+                for (int g = 0; g < R / XG; ++g) {
+                    const float4 x0 = *reinterpret_cast<const float4*>(xs[g] + c), x1 = *reinterpret_cast<const float4*>(xs[g] + c + 4);
+                    const float xv[8] = {x0.x, x0.y, x0.z, x0.w, x1.x, x1.y, x1.z, x1.w};
+#pragma unroll
+                    for (int q = 0; q < XG; ++q) {
+                        const int r = g * XG + q;
+                        const __nv_bfloat162* p = reinterpret_cast<const __nv_bfloat162*>(&raw[d][r]);
+#pragma unroll
+                        for (int i = 0; i < 4; ++i) {
+                            const float2 f = __bfloat1622float2(p[i]);
+                            a[r] = fmaf(f.x, xv[2 * i], a[r]);
+                            a[r] = fmaf(f.y, xv[2 * i + 1], a[r]);
+                        }
                     }
                 }
             }
@@ -218,7 +228,7 @@ moe_pair_down_kernel(const TA* __restrict__ act, const TW* __restrict__ Wd, cons
         }
         const float* const av[2] = {as + (size_t)k * F, as + (size_t)k1 * F};
         float d[8];
-        lane_dot_rows<TW, 8, 4>(rows, av, F, lane, d);
+        lane_dot_rows<TW, 8, 4, 2>(rows, av, F, lane, d);
         const float w0 = wts[(size_t)t * top + k], w1 = wts[(size_t)t * top + k1];
 #pragma unroll
         for (int q = 0; q < 4; ++q) {

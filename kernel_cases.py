@@ -215,6 +215,19 @@ def case(name):
         pairs = sum(c + j + 1 for c, n in reqs for j in range(n))
         return (lambda: latent_attention(q, cache, g, batch, Hh, C, R, ps, (C + R) ** -0.5)), \
             pairs * (C + R) * 2 // max(1, T // len(reqs)), 2 * pairs * Hh * (2 * C + R)
+    if name == "routed_pairs_decode":
+        # routed experts, one token: 2 of 8 experts of [7168 x 4096] gate, up and down matrices, each (token, expert) pair streaming
+        # its expert's rows once (352 MB read, far more than L2 holds); router included
+        from forge_b200.kernels import moe_pairs, moe_route
+        W_, F_, E_, top = 4096, 7168, 8, 2
+        x = _bf16(1, W_)
+        router = torch.randn(E_, W_, device=DEV) * 0.02
+        gate_up, down = _bf16(E_, 2 * F_, W_, scale=0.02), _bf16(E_, W_, F_, scale=0.02)
+
+        def run():
+            idx, wts = moe_route(x, router, top)
+            moe_pairs(x, idx, wts, gate_up, down)
+        return run, top * 3 * W_ * F_ * 2, top * 3 * W_ * F_ * 2
     if name == "retention_scan":
         # the retention recurrence alone: one request of 1,024 tokens, 32 heads of 64 key and 64 value channels (4 FLOPs per
         # state element and token), with the kernel that rotates q and k in front of it
@@ -234,7 +247,7 @@ def case(name):
             kk.copy_(k0)
             retention_scan((qq, 0), (kk, 0), (v, 0), batch, freq, K ** -0.5, decay, state, N, K, K)
         return run, 3 * T * N * K * 4, 4 * T * N * K * K
-    raise SystemExit(f"unknown case {name!r}; known: latent_attention_prefill latent_attention_prefill_512 latent_attention_decode retention_scan scored_attention_prefill scored_attention_decode distance_attention_prefill state_scan_gated headmix_attention_prefill headmix_attention_decode state_scan_wkv state_scan_delta "
+    raise SystemExit(f"unknown case {name!r}; known: routed_pairs_decode latent_attention_prefill latent_attention_prefill_512 latent_attention_decode retention_scan scored_attention_prefill scored_attention_decode distance_attention_prefill state_scan_gated headmix_attention_prefill headmix_attention_decode state_scan_wkv state_scan_delta "
                      "gemm_decode_gateup gemm_decode_down gemm_decode_lmhead gemm_prefill_qkv "
                      "gemm_prefill_gateup "
                      "gemm_prefill_qkv_rope gemm_prefill_down attention_decode attention_decode_fused attention_decode_stream attention_prefill "

@@ -339,6 +339,35 @@ def test_routed_experts_alone(dtype, W, F, E, top, T):
     assert max_rel_err(res.cpu()[clear], (r0.double() + want)[clear]) <= PART_TOL[dtype]
 
 
+@pytest.mark.parametrize("T", [4, 11, 127])
+def test_experts_that_nobody_chose_run_no_product(T):
+    """bfloat16 steps below the ranked path's size give every expert room for the step's tokens and skip, on the device, the products
+    of an expert without tokens: five of eight experts can never be chosen here (one input channel is constant and their router rows
+    weigh it down), and whatever their rows of the buffers hold must not show."""
+    from forge_b200.config import PartSpec
+    from forge_b200.parts import build_part
+    W, F, E, top = 64, 32, 8, 2
+    ff = build_part("feed_forward", PartSpec("routed_experts", {"hidden_size": W, "intermediate_size": F, "experts": E, "top": top}),
+                    _rt(torch.bfloat16))
+    t = {n: rand(*s.shape, seed=40 + i, scale=0.3).to(torch.bfloat16) for i, (n, s) in enumerate(ff.tensor_specs().items())}
+    t["mlp.router"][3:, 0] = -6.0
+    ff.bind(t)
+    assert ff.gate_up_of[0].tensor_core and T * top >= E
+    x = rand(T, W, seed=T, scale=1.0)
+    x[:, 0] = 4.0
+    x = x.to(torch.bfloat16)
+    w = {k.split("mlp.", 1)[1]: v.double() for k, v in t.items()}
+    s_ = torch.sigmoid(x.double() @ w["router"].t())
+    assert bool((s_[:, 3:].max(dim=1).values < s_[:, :3].sort(dim=1, descending=True).values[:, top - 1]).all())
+    srt = s_.sort(dim=-1, descending=True).values
+    clear = (srt[:, top - 1] - srt[:, top]) > 1e-2
+    assert int(clear.sum()) >= max(1, T // 2)
+    want = PZ.routed_ff(x.double(), w, {"router": {"experts": E, "top": top}})
+    for _ in range(2):                                                      # the second time over buffers that the first left filled
+        got = ff.forward(x.to(DEV), None).cpu()
+        assert torch.isfinite(got).all() and max_rel_err(got[clear], want[clear]) <= PART_TOL[torch.bfloat16]
+
+
 def test_router_scores_are_not_renormalised_and_the_lower_index_wins_a_tie():
     from forge_b200 import kernels
     router = torch.zeros(6, 8)
