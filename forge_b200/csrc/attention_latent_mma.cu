@@ -53,7 +53,7 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
 // tokens): run sp leaves its sums as they are in u fp32 [nsplit, T, H, C], beside the row's maximum (in units of log2 e) and
 // sum in part_ml [nsplit, T, H, 2].
 template <int VC, bool SPLIT>
-__global__ void __launch_bounds__(kThreads)
+__global__ void __launch_bounds__(2 * kThreads)
 latent_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ cache, const int32_t* __restrict__ block_table,
                   const int32_t* __restrict__ tok_req, const int32_t* __restrict__ positions, const int32_t* __restrict__ tile_t0,
                   const int32_t* __restrict__ tile_n, float* __restrict__ u, __nv_bfloat16* __restrict__ out, float* __restrict__ part_ml,
@@ -63,7 +63,11 @@ latent_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __re
     forge::pdl_wait();
     const int nsplit = SPLIT ? nsplit_given : 1;
     // the last tiles of a prompt see the most keys: they start first, so that the short ones fill the grid's tail
-    const int tile = gridDim.x / nsplit - 1 - blockIdx.x / nsplit, sp = blockIdx.x % nsplit, v0 = blockIdx.z * VC;
+    // A CTA of eight warps (prompt portions whose latent has an even number of value chunks) is two sets of four over the same
+    // queries and tiles of rows, each set with a chunk of value columns of its own: twice the warps for the copies' latency to hide behind.
+    const int nthreads = blockDim.x, halves = nthreads / kThreads;
+    const int tile = gridDim.x / nsplit - 1 - blockIdx.x / nsplit, sp = blockIdx.x % nsplit;
+    const int v0 = (blockIdx.z * halves + (int)(threadIdx.x / kThreads)) * VC;
     const int t0 = tile_t0 ? tile_t0[tile] : tile;
     const int nq = tile_n ? tile_n[tile] : 1;
     if (!FORGE_TOKEN_OK(t0) || !FORGE_TOKEN_OK(t0 + nq - 1)) return;
@@ -73,12 +77,12 @@ latent_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __re
     __nv_bfloat16* Qs = reinterpret_cast<__nv_bfloat16*>(smem_raw);      // [qrows][KD + 8]
     __nv_bfloat16* Ks = Qs + qrows * KP;                                  // nbuf x [BN][KD + 8]
     const int stage = BN * KP;
-    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int tid = threadIdx.x, lane = tid & 31, warp = (tid >> 5) & 3;
     const uint4 zero4 = make_uint4(0, 0, 0, 0);
 
     // queries: row r = token t0 + r / nh, head h0 + r % nh
     const int dchunks = KD >> 3;
-    for (int i = tid; i < qrows * dchunks; i += kThreads) {
+    for (int i = tid; i < qrows * dchunks; i += nthreads) {
         const int r = i / dchunks, ch = i % dchunks;
         uint4 val = zero4;
         if (r < rows) val = *reinterpret_cast<const uint4*>(q + ((size_t)(t0 + r / nh) * H + h0 + r % nh) * KD + ch * 8);
@@ -105,7 +109,7 @@ latent_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __re
     int page_shift = 0;
     while ((1 << page_shift) < page_size) ++page_shift;
 
-    const int frow = tid >> 1, fpar = tid & 1;                            // two threads a cache row
+    const int per_row = nthreads / BN, frow = tid / per_row, fpar = tid % per_row;   // two (or four) threads a cache row
     auto fetch = [&](int kt, int buf) {
         const int j = kt * BN + frow;
         __nv_bfloat16* Kb = Ks + buf * stage + frow * KP;
@@ -118,7 +122,7 @@ latent_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __re
                 src = cache + ((size_t)page * page_size + (j & (page_size - 1))) * KD;
             }
         }
-        for (int ch = fpar; ch < dchunks; ch += 2) copy16_async(Kb + ch * 8, ok ? src + ch * 8 : cache, ok);
+        for (int ch = fpar; ch < dchunks; ch += per_row) copy16_async(Kb + ch * 8, ok ? src + ch * 8 : cache, ok);
         copies_commit();
     };
     const int n_tiles = last_tile + 1, per = (n_tiles + nsplit - 1) / nsplit, kt_lo = sp * per, kt_hi = min(n_tiles, kt_lo + per);
@@ -242,7 +246,7 @@ latent_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __re
         const int r = h ? r_hi : r_lo;
         if (r >= rows || rb * 16 >= rows) continue;
         const size_t head_index = (size_t)sp * T * H + (size_t)(t0 + r / nh) * H + h0 + r % nh;
-        if (nsplit > 1 && blockIdx.z == 0 && (lane & 3) == 0 && (!colsplit || warp == 0)) {
+        if (nsplit > 1 && v0 == 0 && (lane & 3) == 0 && (!colsplit || warp == 0)) {
             part_ml[head_index * 2] = row_m[h];
             part_ml[head_index * 2 + 1] = row_l[h];
         }
@@ -303,7 +307,7 @@ forge::PerDeviceFlag g_attr_done[6];
 template <int VC, bool SPLIT>
 int launch_latent(int which, dim3 grid, size_t smem, cudaStream_t stream, const __nv_bfloat16* q, const __nv_bfloat16* cache, const int32_t* bt,
                   const int32_t* tok_req, const int32_t* positions, const int32_t* t0, const int32_t* tn, float* u, __nv_bfloat16* out,
-                  float* part_ml, int nsplit, int nbuf, int T, int qrows, int H, int HG, int C, int R, int page_size, int max_pages, float scale) {
+                  float* part_ml, int nsplit, int nbuf, int T, int qrows, int H, int HG, int C, int R, int page_size, int max_pages, float scale, int halves) {
     bool& done = g_attr_done[which + (SPLIT ? 3 : 0)].current();
     if (!done) {
         cudaError_t e = cudaFuncSetAttribute(latent_mma_kernel<VC, SPLIT>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemLimit);
@@ -311,7 +315,7 @@ int launch_latent(int which, dim3 grid, size_t smem, cudaStream_t stream, const 
         done = true;
     }
     return forge::check_launch("latent_attention_mma",
-                               forge::launch(latent_mma_kernel<VC, SPLIT>, grid, dim3(kThreads), smem, stream, 1, q, cache, bt, tok_req, positions, t0,
+                               forge::launch(latent_mma_kernel<VC, SPLIT>, grid, dim3(kThreads * halves), smem, stream, 1, q, cache, bt, tok_req, positions, t0,
                                              tn, u, out, part_ml, nsplit, nbuf, T, qrows, H, HG, C, R, page_size, max_pages, scale));
 }
 
@@ -350,12 +354,14 @@ extern "C" int forge_latent_attention_mma(const void* q, const void* cache, cons
     const int qrows = (tile_t0 == nullptr && HG <= 16) ? 16 : BM;
     const int nbuf = latent_mma_smem(qrows, KD, 2) <= (size_t)kSmemLimit ? 2 : 1;
     const size_t smem = latent_mma_smem(qrows, KD, nbuf);
-    const dim3 grid(num_tiles * nsplit, (H + HG - 1) / HG, chunks);
+    // prompt portions over a latent of an even number of value chunks: a CTA of eight warps takes two chunks
+    const int halves = (tile_t0 != nullptr && nsplit == 1 && chunks % 2 == 0) ? 2 : 1;
+    const dim3 grid(num_tiles * nsplit, (H + HG - 1) / HG, chunks / halves);
     const __nv_bfloat16* qb = (const __nv_bfloat16*)q;
     const __nv_bfloat16* cb = (const __nv_bfloat16*)cache;
     __nv_bfloat16* ob = (__nv_bfloat16*)out;
     int rc;
-#define FORGE_LATENT_ARGS grid, smem, stream, qb, cb, block_table, tok_req, positions, tile_t0, tile_n, u, ob, part_ml, nsplit, nbuf, T, qrows, H, HG, C, R, page_size, max_pages, scale
+#define FORGE_LATENT_ARGS grid, smem, stream, qb, cb, block_table, tok_req, positions, tile_t0, tile_n, u, ob, part_ml, nsplit, nbuf, T, qrows, H, HG, C, R, page_size, max_pages, scale, halves
     if (nsplit > 1) rc = VC == 64 ? launch_latent<64, true>(0, FORGE_LATENT_ARGS) : VC == 128 ? launch_latent<128, true>(1, FORGE_LATENT_ARGS) : launch_latent<256, true>(2, FORGE_LATENT_ARGS);
     else rc = VC == 64 ? launch_latent<64, false>(0, FORGE_LATENT_ARGS) : VC == 128 ? launch_latent<128, false>(1, FORGE_LATENT_ARGS) : launch_latent<256, false>(2, FORGE_LATENT_ARGS);
 #undef FORGE_LATENT_ARGS

@@ -197,6 +197,8 @@ LATENT = {
     # sizes that the tensor-core kernel takes in bfloat16, fed in portions that cross its tiles
     "wide": dict(num_heads=8, head_dim=32, rot_dim=16, v_head_dim=48, kv_rank=96, q_rank=64, scale=0.15, theta=250000.0,
                  scaling={"factor": 8.0, "original": 128, "fast": 16.0, "slow": 2.0}, tokens=150, cuts=LONG_CUTS),
+    "latent_of_two_value_chunks": dict(num_heads=6, head_dim=16, rot_dim=16, v_head_dim=24, kv_rank=416, q_rank=32, scale=0.2, theta=5e3,
+                                       scaling=None, tokens=150, cuts=LONG_CUTS),
     "wide_latent_of_128": dict(num_heads=5, head_dim=24, rot_dim=32, v_head_dim=16, kv_rank=128, q_rank=48, scale=0.2, theta=1e4, scaling=None,
                                tokens=150, cuts=LONG_CUTS),
 }
@@ -267,7 +269,8 @@ def test_a_layer_reads_the_rows_that_another_layer_cached(dtype):
 
 @pytest.mark.parametrize("dtype", DT)
 @pytest.mark.parametrize("page_size", [8, 64])
-@pytest.mark.parametrize("C, R, H", [(6, 2, 2), (96, 16, 8)])        # the second is a shape that the tensor-core kernel takes in bfloat16
+# the second is a shape that the tensor-core kernel takes in bfloat16, the third one whose value columns it takes in two chunks (eight warps)
+@pytest.mark.parametrize("C, R, H", [(6, 2, 2), (96, 16, 8), (448, 32, 4)])
 def test_one_row_that_stands_out(dtype, page_size, C, R, H):
     """Latent rows are zero except one whose score is huge for head 0; a row's second channel carries its position, its third
     is one.  Head 0 returns the row's position if the token sees it (far back among hundreds, at a page's border, the token
@@ -316,9 +319,12 @@ def test_one_row_that_stands_out(dtype, page_size, C, R, H):
 # ----------------------------------------------------------------------------------------------- routed experts
 
 @pytest.mark.parametrize("dtype", DT)
-@pytest.mark.parametrize("W, F, E, top, T", [(40, 24, 5, 1, 19), (40, 100, 3, 3, 19), (64, 16, 8, 2, 3), (64, 48, 6, 2, 300), (192, 128, 4, 3, 130)])
+@pytest.mark.parametrize("W, F, E, top, T", [(40, 24, 5, 1, 19), (40, 100, 3, 3, 19), (64, 16, 8, 2, 3), (64, 48, 6, 2, 300), (192, 128, 4, 3, 130),
+                                             (64, 16, 8, 1, 3), (64, 16, 8, 3, 2), (40, 24, 5, 1, 2), (64, 24, 10, 3, 3), (72, 40, 7, 2, 1),
+                                             (520, 264, 12, 5, 2)])
 def test_routed_experts_alone(dtype, W, F, E, top, T):
-    """Few tokens (every pair on its own) and many (pairs ranked by expert), one expert, all experts."""
+    """Few tokens (every pair on its own, an odd and an even number of experts a token, rows longer than a warp's pass), some more (room
+    for the step's tokens per expert) and many (pairs ranked by expert), one expert, all experts."""
     from forge_b200.config import PartSpec
     from forge_b200.parts import build_part
     ff = build_part("feed_forward", PartSpec("routed_experts", {"hidden_size": W, "intermediate_size": F, "experts": E, "top": top}), _rt(dtype))
