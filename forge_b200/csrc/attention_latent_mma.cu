@@ -9,7 +9,8 @@
 // queries, else through one.  mma.sync m16n8k16 (the legacy tensor path).  Softmax in fp32 with a running maximum and sum
 // per row in registers; a weight is the value product's operand as two bfloat16 numbers, its rounding and what the
 // rounding left over (16 bits of mantissa).  A step of single tokens may deal a request's tiles out to several CTAs in
-// runs; a second kernel puts the runs together.
+// runs; a second kernel puts the runs together.  Where the latent has an even number of value chunks, a prompt's CTA is
+// eight warps: two sets of four over the same queries and tiles, each with a chunk of its own.
 #include "common.cuh"
 #include "checks.cuh"
 
