@@ -408,6 +408,19 @@ moe_combine_kernel(const float* __restrict__ ys, const int32_t* __restrict__ des
     forge::pdl_launch_dependents();
     forge::pdl_wait();
     const int t = blockIdx.x;
+    if ((W & 3) == 0 && (((uintptr_t)ys | (uintptr_t)y) & 15) == 0) {          // four channels a load, the experts in the same order
+#pragma unroll 4
+        for (int c = threadIdx.x * 4; c < W; c += 512) {
+            float4 sum = make_float4(0.f, 0.f, 0.f, 0.f);
+            for (int k = 0; k < top; ++k) {
+                const float w = wts[(size_t)t * top + k];
+                const float4 v = *reinterpret_cast<const float4*>(ys + (size_t)dest[(size_t)t * top + k] * W + c);
+                sum.x = fmaf(w, v.x, sum.x); sum.y = fmaf(w, v.y, sum.y); sum.z = fmaf(w, v.z, sum.z); sum.w = fmaf(w, v.w, sum.w);
+            }
+            *reinterpret_cast<float4*>(y + (size_t)t * W + c) = sum;
+        }
+        return;
+    }
     for (int c = threadIdx.x; c < W; c += 128) {
         float sum = 0.f;
         for (int k = 0; k < top; ++k) sum = fmaf(wts[(size_t)t * top + k], ys[(size_t)dest[(size_t)t * top + k] * W + c], sum);
