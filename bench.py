@@ -536,12 +536,12 @@ def tuzavik_shape(width, layers, heads, dim, ff, state_heads, state_dim, vocab, 
     ``dim`` value channels over a latent of 4*dim channels, queries through a latent of 3/4 of the width), two retention layers and a
     latent attention that reads the first one's rows, in turn; the feed-forward is dense and routed in turn (8 experts of half the
     dense width, 2 a token, so that a token passes through as many feed-forward weights as in the other decoders)."""
-    rot = {"dims": dim // 2, "base": 10000.0, "scaling": {"factor": 8.0, "original": 1024, "fast": 32.0, "slow": 1.0}}
+    rot = {"dims": dim // 2, "base": 10000.0, "scaling": {"factor": 4.0, "original": 2048, "fast": 16.0, "slow": 2.0}}
     lat = lambda src: {"type": "latent_attention", "mixer": dict({"heads": heads, "dim": dim, "rot_dim": dim // 2, "vdim": dim, "kv_rank": 4 * dim,
                                                                  "q_rank": 3 * width // 4, "scale": (dim + dim // 2) ** -0.5, "rot": rot},
                                                                 **({} if src is None else {"kv_from": src}))}
     ret = {"type": "retention", "mixer": {"heads": state_heads, "dim": state_dim, "vdim": state_dim, "rot": {"dims": state_dim, "base": 10000.0},
-                                          "decay": [1.0 - 2.0 ** (-5.0 - 5.0 * n / max(1, state_heads - 1)) for n in range(state_heads)]}}
+                                          "decay": [1.0 - 2.0 ** (-4.0 - 6.0 * n / max(1, state_heads - 1)) for n in range(state_heads)]}}
     dense = {"kind": "dense", "ff": ff}
     moe = {"kind": "moe", "expert": {"ff": ff // 2}, "router": {"experts": 8, "top": 2}}
     out = []
@@ -549,8 +549,8 @@ def tuzavik_shape(width, layers, heads, dim, ff, state_heads, state_dim, vocab, 
         kind = i % 4
         layer = lat(None) if kind == 0 else (lat(i - 3) if kind == 3 else ret)
         out.append(dict(layer, mlp=dense if i % 2 == 0 else moe))
-    return {"architecture": "Tuzavik", "vocab": vocab, "width": width, "norm": {"eps": 1e-5}, "residual_mult": 0.5, "logit_scale": 0.5,
-            "embedding": {"bigram": {"buckets": 8191, "mul_prev": 31, "mul_cur": 7}}, "max_positions": 8192, "layers": out}
+    return {"architecture": "Tuzavik", "vocab": vocab, "width": width, "norm": {"eps": 1e-5}, "residual_mult": 0.5, "logit_scale": 0.4,
+            "embedding": {"bigram": {"buckets": 8191, "mul_prev": 40503, "mul_cur": 9973}}, "max_positions": 8192, "layers": out}
 
 
 def tuzavik_matmul_params(cfg, experts_read=None):
