@@ -7,7 +7,9 @@
 //               device memory, so the path can be replayed in a CUDA graph; it is the path of steps with few tokens
 //   sorted      for steps of many tokens: the pairs are ranked by (expert, token) so that each expert's tokens are
 //               consecutive rows, the rows go through ordinary matrix products expert by expert, and a last kernel adds a
-//               token's experts up in the router's order
+//               token's experts up in the router's order.  The rows lie packed (the caller reads the counts) or, for steps
+//               that must not wait for the device, with room for a step's tokens per expert: expert e's rows from e * cap
+//               on, the products of an expert without rows skipped on the device by its count
 //
 // Router arithmetic is fp32 whatever the activations' type.  Every sum has a fixed order: a dot product is dealt to the
 // lanes of a warp by index and summed by the butterfly, a token's experts are added in the order of their scores.
