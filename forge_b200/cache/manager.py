@@ -23,6 +23,7 @@ class GroupSpec:
     num_pages: int
     window: Optional[int] = None      # None: all positions are kept
     keep_first: int = 0               # with a window: the first positions of a sequence stay readable for good
+    chunk: Optional[int] = None       # a position reads only its own chunk of this many positions (counted from position 0)
 
 
 @dataclass
@@ -116,16 +117,21 @@ class CacheManager:
     def release_out_of_window(self, req_id):
         """After a step: gives back the pages of windowed groups that no future query can read.  The next
         query is at position >= num_tokens and reads keys > position - window, so a page whose last
-        position is <= num_tokens - window is dead, unless it holds one of the group's kept first positions.  Returns the number of pages released."""
+        position is <= num_tokens - window is dead, unless it holds one of the group's kept first positions.  In a chunked group the
+        next query reads no key before the start of the chunk that position num_tokens lies in.  Returns the number of pages released."""
         r = self._requests[req_id]
         released = 0
         for g, spec in self.groups.items():
-            if spec.window is None:
+            if spec.window is None and spec.chunk is None:
                 continue
             table = r.tables[g]
-            first_needed = r.num_tokens - spec.window + 1          # smallest key position a future query reads
+            first_needed = 0                                        # smallest key position a future query reads
+            if spec.window is not None:
+                first_needed = max(first_needed, r.num_tokens - spec.window + 1)
+            if spec.chunk is not None:
+                first_needed = max(first_needed, r.num_tokens // spec.chunk * spec.chunk)
             dead_pages = max(0, first_needed) // self.page_size     # pages wholly below it
-            kept_pages = self._pages_for(spec.keep_first)           # pages that hold a position every query may read
+            kept_pages = self._pages_for(spec.keep_first) if spec.window is not None else 0      # pages every query may read
             for i in range(kept_pages, min(dead_pages, len(table))):
                 if table[i] >= 0:
                     self.pools[g].release(table[i], req_id)

@@ -31,6 +31,8 @@ class LayerCache:
 
 def group_name(spec: KVCacheSpec):
     w = "full" if spec.window is None else f"win{spec.window}" + (f"+first{spec.keep_first}" if spec.keep_first else "")
+    if spec.chunk is not None:
+        w += f"_chunk{spec.chunk}"
     v = "" if spec.value_dim == spec.head_dim else f"v{spec.value_dim}"
     return f"kv{spec.num_kv_heads}x{spec.head_dim}{v}_{w}"
 
@@ -93,7 +95,7 @@ class CacheStorage:
         groups, self.layer_group = plan_groups(cache_specs, cache_from)
         if isinstance(pages_per_group, int):
             pages_per_group = {g: pages_per_group for g in groups}
-        self.manager = CacheManager([GroupSpec(g, pages_per_group[g], s.window, s.keep_first) for g, s in groups.items()],
+        self.manager = CacheManager([GroupSpec(g, pages_per_group[g], s.window, s.keep_first, s.chunk) for g, s in groups.items()],
                                     page_size, max_requests)
         self.page_size, self.max_requests, self.dtype, self.device = page_size, max_requests, dtype, device
         self.layers = []

@@ -3,6 +3,7 @@ from .llama import LlamaConfig
 from .zatupel import ZatupelConfig
 from .tidenex import TidenexConfig
 from .tuzavik import TuzavikConfig
+from .natalorn import NatalornConfig
 from .registry import (config_from_dict, load_config, register_architecture, registered_architectures,
                        unregister_architecture)
 
@@ -21,5 +22,9 @@ register_architecture("Tidenex", TidenexConfig, replace=True)
 # dense or routed feed-forwards, an embedding that also looks at the token before
 register_architecture("Tuzavik", TuzavikConfig, replace=True)
 
-__all__ = ["ZatupelConfig", "TidenexConfig", "TuzavikConfig", "ConfigError", "LayerSpec", "ModelPlan", "PartSpec", "LlamaConfig", "config_from_dict", "load_config",
+# pre-norm layers on a residual stream kept as several copies (hyper-connections): windowed and chunked attention without rotation,
+# attention over one cached latent per token with a sink and a gate, routed experts chosen within groups beside a shared expert
+register_architecture("Natalorn", NatalornConfig, replace=True)
+
+__all__ = ["ZatupelConfig", "TidenexConfig", "TuzavikConfig", "NatalornConfig", "ConfigError", "LayerSpec", "ModelPlan", "PartSpec", "LlamaConfig", "config_from_dict", "load_config",
            "register_architecture", "registered_architectures", "unregister_architecture"]

@@ -52,6 +52,9 @@ class ModelPlan:
     lm_head_prefix: str = "lm_head."
     # positions of the schedule before whose layer the embedding output is added to the residual stream again
     add_embedding_before: tuple = ()
+    # the residual stream is kept as this many copies (all equal to the embedding output at the start; the final norm reads their
+    # sum); the layers' blocks then work on rows of streams * hidden_size numbers
+    streams: int = 1
 
 
 def require(d, key, typ):

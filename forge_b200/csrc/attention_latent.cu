@@ -70,7 +70,7 @@ template <typename TI, typename TW, typename TO>
 __global__ void __launch_bounds__(kLinThreads)
 head_linear_kernel(const TI* __restrict__ in, long long in_ld, int in_hs, const TW* __restrict__ W, TO* __restrict__ out,
                    long long out_ld, int out_hs, const int32_t* __restrict__ positions, const float* __restrict__ freq, float amp,
-                   int T, int K, int N, int R) {
+                   int T, int K, int N, int R, const float* __restrict__ gate, long long gate_ld) {
     extern __shared__ float xs[];                       // [kLinTokens][K]
     forge::pdl_launch_dependents();
     forge::pdl_wait();
@@ -93,7 +93,11 @@ head_linear_kernel(const TI* __restrict__ in, long long in_ld, int in_hs, const 
         }
 #pragma unroll
         for (int tt = 0; tt < kLinTokens; ++tt)
-            if (tt < nt) out[(size_t)(t0 + tt) * out_ld + (size_t)h * out_hs + n] = forge::from_float<TO>(acc[tt]);
+            if (tt < nt) {
+                float v = acc[tt];
+                if (gate) v *= 1.0f / (1.0f + expf(-gate[(size_t)(t0 + tt) * gate_ld + (size_t)h * N + n]));
+                out[(size_t)(t0 + tt) * out_ld + (size_t)h * out_hs + n] = forge::from_float<TO>(v);
+            }
     }
     if (R > 0 && blockIdx.z == 0) {
         for (int i = threadIdx.x; i < nt * (R >> 1); i += kLinThreads) {
@@ -145,7 +149,7 @@ template <typename TI>
 __global__ void __launch_bounds__(kHlmThreads)
 head_linear_mma_kernel(const TI* __restrict__ in, long long in_ld, int in_hs, const __nv_bfloat16* __restrict__ W, __nv_bfloat16* __restrict__ out,
                        long long out_ld, int out_hs, const int32_t* __restrict__ positions, const float* __restrict__ freq, float amp,
-                       int T, int K, int N, int R) {
+                       int T, int K, int N, int R, const float* __restrict__ gate, long long gate_ld) {
     __shared__ __align__(16) __nv_bfloat16 As[kHlmTile][kHlmRowK];         // [token][input channel of the chunk]
     __shared__ __align__(16) __nv_bfloat16 Bs[kHlmK][kHlmRow];             // [input channel of the chunk][output channel]
     forge::pdl_launch_dependents();
@@ -208,8 +212,14 @@ head_linear_mma_kernel(const TI* __restrict__ in, long long in_ld, int in_hs, co
             const int t = t0 + warp * 16 + (lane >> 2) + half * 8;
             if (t >= T) continue;
             __nv_bfloat16* dst = out + (size_t)t * out_ld + (size_t)h * out_hs + n;
-            if (n < N) dst[0] = __float2bfloat16(acc[nb][2 * half]);
-            if (n + 1 < N) dst[1] = __float2bfloat16(acc[nb][2 * half + 1]);
+            float v0 = acc[nb][2 * half], v1 = acc[nb][2 * half + 1];
+            if (gate) {
+                const float* gr = gate + (size_t)t * gate_ld + (size_t)h * N + n;
+                if (n < N) v0 *= 1.0f / (1.0f + expf(-gr[0]));
+                if (n + 1 < N) v1 *= 1.0f / (1.0f + expf(-gr[1]));
+            }
+            if (n < N) dst[0] = __float2bfloat16(v0);
+            if (n + 1 < N) dst[1] = __float2bfloat16(v1);
         }
     }
     if (R > 0 && blockIdx.z == 0) {
@@ -237,7 +247,7 @@ __global__ void __launch_bounds__(kAttThreads)
 latent_attention_kernel(const TC* __restrict__ q, const TC* __restrict__ cache, const int32_t* __restrict__ block_table,
                         const int32_t* __restrict__ tok_req, const int32_t* __restrict__ positions,
                         const int32_t* __restrict__ tile_t0, const int32_t* __restrict__ tile_n, TC* __restrict__ out, int H, int HG,
-                        int C, int R, int page_size, int max_pages, float scale, int TQ, int KT) {
+                        int C, int R, int page_size, int max_pages, float scale, int TQ, int KT, int window, const float* __restrict__ sink) {
     extern __shared__ float smem[];
     forge::pdl_launch_dependents();
     forge::pdl_wait();
@@ -265,7 +275,8 @@ latent_attention_kernel(const TC* __restrict__ q, const TC* __restrict__ cache, 
     for (int i = tid; i < rows * C; i += kAttThreads) acc[i] = 0.f;
     for (int i = tid; i < rows; i += kAttThreads) { ms[i] = -INFINITY; ls[i] = 0.f; }
 
-    for (int j0 = 0; j0 <= pos_last; j0 += KT) {
+    // chunks of rows that lie behind the window of every token of the tile are skipped: they would add exact zeros
+    for (int j0 = (window > 0 ? max(0, pos0 - window + 1) : 0) / KT * KT; j0 <= pos_last; j0 += KT) {
         __syncthreads();                                  // the chunk before is done with ks and sc
         for (int i = tid; i < KT * KD; i += kAttThreads) {
             const int c = i % KD, jj = i / KD, j = j0 + jj;
@@ -280,7 +291,7 @@ latent_attention_kernel(const TC* __restrict__ q, const TC* __restrict__ cache, 
         for (int i = tid; i < rows * KT; i += kAttThreads) {
             const int jj = i % KT, row = i / KT, tq = row / nh;
             float s = -INFINITY;
-            if (j0 + jj <= pos0 + tq) {
+            if (j0 + jj <= pos0 + tq && (window <= 0 || pos0 + tq - (j0 + jj) < window)) {
                 const float* qr = qs + row * KD;
                 const float* kr = ks + jj * KP;
                 s = 0.f;
@@ -326,7 +337,9 @@ latent_attention_kernel(const TC* __restrict__ q, const TC* __restrict__ cache, 
     __syncthreads();
     for (int i = tid; i < rows * C; i += kAttThreads) {
         const int c = i % C, row = i / C, hh = row % nh, tq = row / nh;
-        out[((size_t)(t0 + tq) * H + h0 + hh) * C + c] = forge::from_float<TC>(acc[i] / ls[row]);
+        // a sink joins the denominator as one more weight, exp(sink_h), that has no row of its own
+        const float den = sink ? ls[row] + expf(sink[h0 + hh] - ms[row]) : ls[row];
+        out[((size_t)(t0 + tq) * H + h0 + hh) * C + c] = forge::from_float<TC>(acc[i] / den);
     }
 }
 
@@ -339,10 +352,11 @@ forge::PerDeviceFlag g_latent_attr[2];
 
 template <typename TI, typename TW, typename TO>
 cudaError_t launch_head_linear(cudaStream_t stream, const void* in, long long in_ld, int in_hs, const void* W, void* out, long long out_ld,
-                               int out_hs, const int32_t* positions, const float* freq, float amp, int T, int H, int K, int N, int R) {
+                               int out_hs, const int32_t* positions, const float* freq, float amp, int T, int H, int K, int N, int R, const float* gate,
+                               long long gate_ld) {
     const dim3 grid((T + kLinTokens - 1) / kLinTokens, H, (N + kLinThreads - 1) / kLinThreads);
     return forge::launch(head_linear_kernel<TI, TW, TO>, grid, dim3(kLinThreads), sizeof(float) * kLinTokens * K, stream, 1, (const TI*)in,
-                         in_ld, in_hs, (const TW*)W, (TO*)out, out_ld, out_hs, positions, freq, amp, T, K, N, R);
+                         in_ld, in_hs, (const TW*)W, (TO*)out, out_ld, out_hs, positions, freq, amp, T, K, N, R, gate, gate_ld);
 }
 
 }  // namespace
@@ -366,10 +380,11 @@ extern "C" int forge_latent_prepare(const float* proj, int ld, const int32_t* po
 
 // out[t, h, 0:N] = sum_k in[t, h, k] W[h, k, n], and (R > 0) out[t, h, N:N+R] = in[t, h, K:K+R] rotated by positions[t].
 // in of in_dtype (fp32 or bf16), W and out of dtype; leading dimensions and head strides in elements.  bf16 weights go to the
-// tensor cores (fp32 inputs rounded to bfloat16 on the way) unless `simt` asks for the fp32 multiply-adds.
+// tensor cores (fp32 inputs rounded to bfloat16 on the way) unless `simt` asks for the fp32 multiply-adds.  gate fp32 (rows of
+// gate_ld, head h's N numbers from h * N) or null: out[t, h, n] is multiplied by sigmoid(gate[t, h, n]).
 extern "C" int forge_head_linear(const void* in, int in_dtype, long long in_ld, int in_hs, const void* W, void* out, int dtype,
                                  long long out_ld, int out_hs, const int32_t* positions, const float* freq, float amp, int T, int H,
-                                 int K, int N, int R, int simt, cudaStream_t stream) {
+                                 int K, int N, int R, int simt, const float* gate, long long gate_ld, cudaStream_t stream) {
     if (T < 0 || H <= 0 || K <= 0 || N <= 0 || R < 0 || (R & 1)) return forge::fail(FORGE_ERR_ARG, "head_linear: bad sizes T=%d H=%d K=%d N=%d R=%d", T, H, K, N, R);
     if (R > 0 && (!positions || !freq)) return forge::fail(FORGE_ERR_ARG, "head_linear: a rotation needs positions and frequencies");
     if (T == 0) return FORGE_OK;
@@ -378,19 +393,19 @@ extern "C" int forge_head_linear(const void* in, int in_dtype, long long in_ld, 
         const dim3 grid((T + kHlmTile - 1) / kHlmTile, H, (N + kHlmTile - 1) / kHlmTile);
         if (in_dtype == FORGE_F32)
             e = forge::launch(head_linear_mma_kernel<float>, grid, dim3(kHlmThreads), 0, stream, 1, (const float*)in, in_ld, in_hs,
-                              (const __nv_bfloat16*)W, (__nv_bfloat16*)out, out_ld, out_hs, positions, freq, amp, T, K, N, R);
+                              (const __nv_bfloat16*)W, (__nv_bfloat16*)out, out_ld, out_hs, positions, freq, amp, T, K, N, R, gate, gate_ld);
         else
             e = forge::launch(head_linear_mma_kernel<__nv_bfloat16>, grid, dim3(kHlmThreads), 0, stream, 1, (const __nv_bfloat16*)in, in_ld, in_hs,
-                              (const __nv_bfloat16*)W, (__nv_bfloat16*)out, out_ld, out_hs, positions, freq, amp, T, K, N, R);
+                              (const __nv_bfloat16*)W, (__nv_bfloat16*)out, out_ld, out_hs, positions, freq, amp, T, K, N, R, gate, gate_ld);
         return forge::check_launch("head_linear (tensor cores)", e);
     }
     if (sizeof(float) * kLinTokens * K > 48 * 1024) return forge::fail(FORGE_ERR_UNSUPPORTED, "head_linear: %d input channels a head", K);
     if (dtype == FORGE_F32 && in_dtype == FORGE_F32)
-        e = launch_head_linear<float, float, float>(stream, in, in_ld, in_hs, W, out, out_ld, out_hs, positions, freq, amp, T, H, K, N, R);
+        e = launch_head_linear<float, float, float>(stream, in, in_ld, in_hs, W, out, out_ld, out_hs, positions, freq, amp, T, H, K, N, R, gate, gate_ld);
     else if (dtype == FORGE_BF16 && in_dtype == FORGE_F32)
-        e = launch_head_linear<float, __nv_bfloat16, __nv_bfloat16>(stream, in, in_ld, in_hs, W, out, out_ld, out_hs, positions, freq, amp, T, H, K, N, R);
+        e = launch_head_linear<float, __nv_bfloat16, __nv_bfloat16>(stream, in, in_ld, in_hs, W, out, out_ld, out_hs, positions, freq, amp, T, H, K, N, R, gate, gate_ld);
     else if (dtype == FORGE_BF16 && in_dtype == FORGE_BF16)
-        e = launch_head_linear<__nv_bfloat16, __nv_bfloat16, __nv_bfloat16>(stream, in, in_ld, in_hs, W, out, out_ld, out_hs, positions, freq, amp, T, H, K, N, R);
+        e = launch_head_linear<__nv_bfloat16, __nv_bfloat16, __nv_bfloat16>(stream, in, in_ld, in_hs, W, out, out_ld, out_hs, positions, freq, amp, T, H, K, N, R, gate, gate_ld);
     else
         return forge::fail(FORGE_ERR_ARG, "head_linear: input type %d with weights of type %d", in_dtype, dtype);
     return forge::check_launch("head_linear", e);
@@ -400,11 +415,12 @@ extern "C" int forge_head_linear(const void* in, int in_dtype, long long in_ld, 
 extern "C" long long forge_latent_attention_smem(int HG, int C, int R, int TQ, int KT) { return (long long)latent_smem_bytes(HG, C, R, TQ, KT); }
 
 // q [T, H, C+R], out [T, H, C] and cache (rows of C + R) of type dtype.  tile_t0 / tile_n int32 [num_tiles] (both null: one
-// token a tile).  HG: heads per CTA.
+// token a tile).  HG: heads per CTA.  window: a position sees the rows of itself and the window - 1 positions before it (0: all);
+// sink fp32 [H] or null: exp(sink_h) joins head h's softmax denominator.
 extern "C" int forge_latent_attention(const void* q, const void* cache, const int32_t* block_table, const int32_t* tok_req,
                                       const int32_t* positions, const int32_t* tile_t0, const int32_t* tile_n, void* out, int dtype,
                                       int num_tiles, int H, int HG, int C, int R, int page_size, int max_pages, float scale, int TQ,
-                                      int KT, cudaStream_t stream) {
+                                      int KT, int window, const float* sink, cudaStream_t stream) {
     if (num_tiles < 0 || H <= 0 || HG <= 0 || C <= 0 || R < 0 || page_size <= 0 || max_pages <= 0 || TQ <= 0 || KT <= 0)
         return forge::fail(FORGE_ERR_ARG, "latent_attention: bad sizes tiles=%d H=%d HG=%d C=%d R=%d page=%d TQ=%d KT=%d", num_tiles, H, HG, C,
                            R, page_size, TQ, KT);
@@ -423,7 +439,7 @@ extern "C" int forge_latent_attention(const void* q, const void* cache, const in
         }
         e = forge::launch(latent_attention_kernel<TT>, dim3(num_tiles, (H + HG - 1) / HG), dim3(kAttThreads), smem, stream, 1, (const TT*)q,
                           (const TT*)cache, block_table, tok_req, positions, tile_t0, tile_n, (TT*)out, H, HG, C, R, page_size, max_pages, scale,
-                          TQ, KT);
+                          TQ, KT, window, sink);
     });
     return forge::check_launch("latent_attention", e);
 }

@@ -58,7 +58,8 @@ __global__ void __launch_bounds__(2 * kThreads)
 latent_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ cache, const int32_t* __restrict__ block_table,
                   const int32_t* __restrict__ tok_req, const int32_t* __restrict__ positions, const int32_t* __restrict__ tile_t0,
                   const int32_t* __restrict__ tile_n, float* __restrict__ u, __nv_bfloat16* __restrict__ out, float* __restrict__ part_ml,
-                  int nsplit_given, int nbuf, int T, int qrows, int H, int HG, int C, int R, int page_size, int max_pages, float scale) {
+                  int nsplit_given, int nbuf, int T, int qrows, int H, int HG, int C, int R, int page_size, int max_pages, float scale,
+                  int window, const float* __restrict__ sink) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
     forge::pdl_launch_dependents();
     forge::pdl_wait();
@@ -103,6 +104,9 @@ latent_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __re
     const int r_lo = rb * 16 + (lane >> 2), r_hi = r_lo + 8;             // this thread's two rows
     const int pos_lo = pos0 + min(r_lo, rows - 1) / nh, pos_hi = pos0 + min(r_hi, rows - 1) / nh;
     const bool live_lo = r_lo < rows, live_hi = r_hi < rows;
+    // the first row each of the thread's two positions sees, and the tile's last token (no token of the tile sees an earlier row)
+    const int see_lo = window > 0 ? max(0, pos_lo - window + 1) : 0, see_hi = window > 0 ? max(0, pos_hi - window + 1) : 0;
+    const int see_last = window > 0 ? max(0, pos_last - window + 1) : 0;
 
     const int last_tile = pos_last / BN;
     constexpr float kLog2e = 1.4426950408889634f;
@@ -126,7 +130,10 @@ latent_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __re
         for (int ch = fpar; ch < dchunks; ch += per_row) copy16_async(Kb + ch * 8, ok ? src + ch * 8 : cache, ok);
         copies_commit();
     };
-    const int n_tiles = last_tile + 1, per = (n_tiles + nsplit - 1) / nsplit, kt_lo = sp * per, kt_hi = min(n_tiles, kt_lo + per);
+    // tiles of rows behind every token's window are skipped: they would add exact zeros
+    const int first_tile = (window > 0 ? max(0, pos0 - window + 1) : 0) / BN;
+    const int n_tiles = last_tile + 1 - first_tile, per = (n_tiles + nsplit - 1) / nsplit, kt_lo = first_tile + sp * per,
+              kt_hi = min(last_tile + 1, kt_lo + per);
     if (kt_lo < kt_hi) fetch(kt_lo, 0);
     for (int kt = kt_lo; kt < kt_hi; ++kt) {
         const int j0 = kt * BN;
@@ -154,7 +161,7 @@ latent_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __re
                 }
             }
             // scale, mask, and the tile's maximum per row.  A tile that every row of the CTA sees whole needs no mask.
-            const bool whole = rows == qrows && qrows == BM && j0 + BN - 1 <= pos0;
+            const bool whole = rows == qrows && qrows == BM && j0 + BN - 1 <= pos0 && j0 >= see_last;
             float tmax[2] = {-INFINITY, -INFINITY};
             if (whole) {
 #pragma unroll
@@ -172,7 +179,7 @@ latent_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __re
                     for (int e = 0; e < 4; ++e) {
                         const int j = j0 + nt * 8 + (lane & 3) * 2 + (e & 1);
                         const int hi = e >> 1;
-                        const bool ok = (hi ? live_hi : live_lo) && j <= (hi ? pos_hi : pos_lo);
+                        const bool ok = (hi ? live_hi : live_lo) && j <= (hi ? pos_hi : pos_lo) && j >= (hi ? see_hi : see_lo);
                         const float s = ok ? sacc[nt][e] * sl2 : -INFINITY;
                         sacc[nt][e] = s;
                         tmax[hi] = fmaxf(tmax[hi], s);
@@ -241,6 +248,14 @@ latent_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __re
         __syncthreads();                                                  // before a later fetch writes into this buffer
         if (nbuf == 1 && kt + 1 < kt_hi) fetch(kt + 1, 0);
     }
+    if (sink != nullptr && nsplit == 1) {
+        // a sink joins the denominator as one more weight, exp(sink_h), that has no row of its own (maxima are in units of log2 e)
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            const int r = min(h ? r_hi : r_lo, rows - 1);
+            if (row_l[h] > 0.f) row_l[h] += ex2(sink[h0 + r % nh] * kLog2e - row_m[h]);
+        }
+    }
     const float inv[2] = {nsplit > 1 ? 1.0f : (row_l[0] > 0.f ? 1.0f / row_l[0] : 0.f), nsplit > 1 ? 1.0f : (row_l[1] > 0.f ? 1.0f / row_l[1] : 0.f)};
 #pragma unroll
     for (int h = 0; h < 2; ++h) {
@@ -264,7 +279,8 @@ latent_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __re
 
 // A warp per (token, head): run s counts with 2^(m_s - m); the sums of all runs over the sum of their weights' sums.
 __global__ void __launch_bounds__(128)
-latent_combine_kernel(const float* __restrict__ u, const float* __restrict__ part_ml, int nsplit, __nv_bfloat16* __restrict__ out, int rows, int C) {
+latent_combine_kernel(const float* __restrict__ u, const float* __restrict__ part_ml, int nsplit, __nv_bfloat16* __restrict__ out, int rows, int C,
+                      const float* __restrict__ sink, int H) {
     constexpr int kMaxSplit = 16;
     forge::pdl_launch_dependents();
     forge::pdl_wait();
@@ -283,6 +299,7 @@ latent_combine_kernel(const float* __restrict__ u, const float* __restrict__ par
             l += wt[s] * part_ml[((size_t)s * rows + w) * 2 + 1];
         }
     }
+    if (sink != nullptr && l > 0.f) l += ex2(sink[w % H] * 1.4426950408889634f - m);      // the sink's weight in the denominator
     const float inv = l > 0.f ? 1.0f / l : 0.f;
     // four channels a load (C is a multiple of 16), all runs' loads of a channel group in flight together
     for (int c = lane * 4; c < C; c += 128) {
@@ -308,7 +325,8 @@ forge::PerDeviceFlag g_attr_done[6];
 template <int VC, bool SPLIT>
 int launch_latent(int which, dim3 grid, size_t smem, cudaStream_t stream, const __nv_bfloat16* q, const __nv_bfloat16* cache, const int32_t* bt,
                   const int32_t* tok_req, const int32_t* positions, const int32_t* t0, const int32_t* tn, float* u, __nv_bfloat16* out,
-                  float* part_ml, int nsplit, int nbuf, int T, int qrows, int H, int HG, int C, int R, int page_size, int max_pages, float scale, int halves) {
+                  float* part_ml, int nsplit, int nbuf, int T, int qrows, int H, int HG, int C, int R, int page_size, int max_pages, float scale, int halves,
+                  int window, const float* sink) {
     bool& done = g_attr_done[which + (SPLIT ? 3 : 0)].current();
     if (!done) {
         cudaError_t e = cudaFuncSetAttribute(latent_mma_kernel<VC, SPLIT>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemLimit);
@@ -317,7 +335,7 @@ int launch_latent(int which, dim3 grid, size_t smem, cudaStream_t stream, const 
     }
     return forge::check_launch("latent_attention_mma",
                                forge::launch(latent_mma_kernel<VC, SPLIT>, grid, dim3(kThreads * halves), smem, stream, 1, q, cache, bt, tok_req, positions, t0,
-                                             tn, u, out, part_ml, nsplit, nbuf, T, qrows, H, HG, C, R, page_size, max_pages, scale));
+                                             tn, u, out, part_ml, nsplit, nbuf, T, qrows, H, HG, C, R, page_size, max_pages, scale, window, sink));
 }
 
 size_t latent_mma_smem(int qrows, int KD, int nbuf) { return sizeof(__nv_bfloat16) * (size_t)(qrows + nbuf * BN) * (KD + kPad); }
@@ -336,11 +354,12 @@ extern "C" int forge_latent_mma_heads(int H) { return H < BM ? H : BM; }
 
 // q bf16 [T, H*(C+R)]; out bf16 [T, H*C]; u fp32 [nsplit, T, H, C] and part_ml fp32 [nsplit, T, H, 2] (scratch, nsplit > 1: steps of
 // single tokens only).  tile_t0 / tile_n: tiles of consecutive tokens of one request with tile_n * min(H, 64) <= 64 (both null:
-// one token per tile, num_tiles = T).
+// one token per tile, num_tiles = T).  window: a position sees the rows of itself and the window - 1 positions before it (0: all);
+// sink fp32 [H] or null: exp(sink_h) joins head h's softmax denominator.
 extern "C" int forge_latent_attention_mma(const void* q, const void* cache, const int32_t* block_table, const int32_t* tok_req,
                                           const int32_t* positions, const int32_t* tile_t0, const int32_t* tile_n, float* u, float* part_ml,
                                           int nsplit, void* out, int T, int num_tiles, int H, int C, int R, int page_size, int max_pages,
-                                          float scale, cudaStream_t stream) {
+                                          float scale, int window, const float* sink, cudaStream_t stream) {
     if (!forge_latent_mma_supports(H, C, R, page_size)) return forge::fail(FORGE_ERR_UNSUPPORTED, "latent_attention_mma: H=%d C=%d R=%d", H, C, R);
     if (T < 0 || num_tiles < 0 || max_pages <= 0 || (tile_t0 == nullptr) != (tile_n == nullptr))
         return forge::fail(FORGE_ERR_ARG, "latent_attention_mma: bad arguments");
@@ -363,14 +382,14 @@ extern "C" int forge_latent_attention_mma(const void* q, const void* cache, cons
     const __nv_bfloat16* cb = (const __nv_bfloat16*)cache;
     __nv_bfloat16* ob = (__nv_bfloat16*)out;
     int rc;
-#define FORGE_LATENT_ARGS grid, smem, stream, qb, cb, block_table, tok_req, positions, tile_t0, tile_n, u, ob, part_ml, nsplit, nbuf, T, qrows, H, HG, C, R, page_size, max_pages, scale, halves
+#define FORGE_LATENT_ARGS grid, smem, stream, qb, cb, block_table, tok_req, positions, tile_t0, tile_n, u, ob, part_ml, nsplit, nbuf, T, qrows, H, HG, C, R, page_size, max_pages, scale, halves, window, sink
     if (nsplit > 1) rc = VC == 64 ? launch_latent<64, true>(0, FORGE_LATENT_ARGS) : VC == 128 ? launch_latent<128, true>(1, FORGE_LATENT_ARGS) : launch_latent<256, true>(2, FORGE_LATENT_ARGS);
     else rc = VC == 64 ? launch_latent<64, false>(0, FORGE_LATENT_ARGS) : VC == 128 ? launch_latent<128, false>(1, FORGE_LATENT_ARGS) : launch_latent<256, false>(2, FORGE_LATENT_ARGS);
 #undef FORGE_LATENT_ARGS
     if (rc != FORGE_OK || nsplit == 1) return rc;
     const unsigned blocks = (unsigned)(((size_t)T * H + 3) / 4);
     return forge::check_launch("latent_combine", forge::launch(latent_combine_kernel, dim3(blocks), dim3(128), 0, stream, 1, (const float*)u,
-                                                               (const float*)part_ml, nsplit, ob, T * H, C));
+                                                               (const float*)part_ml, nsplit, ob, T * H, C, sink, H));
 }
 
 FORGE_DEFINE_CHECKS_ENTRY(attention_latent_mma)

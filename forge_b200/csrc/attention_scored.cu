@@ -6,6 +6,9 @@
 //                   o = a_1 - lambda a_2,   o <- o / sqrt(mean(o^2) + eps) * post          (a_m: map m's output)
 //   distance    score(i, j) = scale q(i) . k(j) - r1_h ln(1 + r2_h (i - j))     (r1 = null: no such term)
 //   out_scale   the head outputs are multiplied by it (a mixer that runs beside another one with weights of their own)
+//   window      position i sees j only if i - j < window                              (0: no such limit)
+//   chunk       position i sees j only if floor(i / chunk) = floor(j / chunk)         (0: no such limit)
+//   softcap     score <- softcap tanh(score / softcap), after the scale                (0: none)
 //
 // and in the prepare step:  an RMS norm over ALL of a token's query channels (and all of its key channels) with a
 // weight per channel; a query temperature 1 + coef ln(floor((p + 1) / every) + 1) at position p; a rotation of the first
@@ -87,6 +90,14 @@ scored_prepare_kernel(const float* __restrict__ proj, int ld, const int32_t* __r
 
 constexpr int kAttThreads = 256;
 
+// The first position that position `pos` sees.  It does not fall as pos grows.
+__device__ __forceinline__ int first_visible(int pos, int window, int chunk) {
+    int lo = 0;
+    if (window > 0) lo = max(lo, pos - window + 1);
+    if (chunk > 0) lo = max(lo, pos / chunk * chunk);
+    return lo;
+}
+
 // One CTA per (tile of up to TQ consecutive tokens of one request, key/value head); tile_t0 = null: tile i is token i.
 // A "row" is one (token, query head of this kv head, map): row = (tq * R + r) * M + m.
 template <typename TC>
@@ -96,7 +107,7 @@ scored_attention_kernel(const TC* __restrict__ q, const TC* __restrict__ cache, 
                         const int32_t* __restrict__ tile_t0, const int32_t* __restrict__ tile_n, const float* __restrict__ r1,
                         const float* __restrict__ r2, TC* __restrict__ out, int H, int G, int M, int D, int E, int page_size,
                         long long page_stride, int max_pages, float scale, float lambda, float post, float eps, float out_scale,
-                        int TQ, int KT, long long out_ld) {
+                        int TQ, int KT, long long out_ld, int window, int chunk, float softcap) {
     extern __shared__ float smem[];
     forge::pdl_launch_dependents();
     forge::pdl_wait();
@@ -126,7 +137,8 @@ scored_attention_kernel(const TC* __restrict__ q, const TC* __restrict__ cache, 
     for (int i = tid; i < rows; i += kAttThreads) { ms[i] = -INFINITY; ls[i] = 0.f; }
 
     const TC* vcache = cache + (size_t)G * page_size * KD;
-    for (int j0 = 0; j0 <= pos_last; j0 += KT) {
+    // chunks of keys that no token of the tile sees are skipped: they would add exact zeros
+    for (int j0 = first_visible(pos0, window, chunk) / KT * KT; j0 <= pos_last; j0 += KT) {
         __syncthreads();                                  // the chunk before is done with ks, vs, sc
         for (int i = tid; i < KT * KD; i += kAttThreads) {
             const int c = i % KD, jj = i / KD, j = j0 + jj;
@@ -153,11 +165,12 @@ scored_attention_kernel(const TC* __restrict__ q, const TC* __restrict__ cache, 
             const int jj = i % KT, row = i / KT, m = row % M, r = (row / M) % R, tq = row / (M * R);
             const int pos = pos0 + tq, j = j0 + jj;
             float s = -INFINITY;
-            if (j <= pos) {
+            if (j <= pos && j >= first_visible(pos, window, chunk)) {
                 const float* qr = qs + row * D;
                 const float* kr = ks + jj * KP + m * D;
                 s = 0.f;
                 for (int d = 0; d < D; ++d) s = fmaf(qr[d], kr[d], s);
+                if (softcap > 0.f) s = softcap * tanhf(s / softcap);
                 if (r1) s -= r1[g * R + r] * log1pf(r2[g * R + r] * (float)(pos - j));
             }
             sc[i] = s;
@@ -263,12 +276,13 @@ extern "C" long long forge_scored_attention_smem(int H, int G, int M, int D, int
 }
 
 // q [T, H*M*D] and out (rows of out_ld elements, the heads' H*E values at their start) in the cache's type.  tile_t0 / tile_n int32 [num_tiles] (both null: one token a tile).
-// r1, r2 fp32 [H] or both null.  M = 2: lambda, post and eps of the combination of the two maps.
+// r1, r2 fp32 [H] or both null.  M = 2: lambda, post and eps of the combination of the two maps.  window, chunk, softcap: 0 = none.
 extern "C" int forge_scored_attention(const void* q, const void* cache, const int32_t* block_table, const int32_t* tok_req,
                                       const int32_t* positions, const int32_t* tile_t0, const int32_t* tile_n, const float* r1,
                                       const float* r2, void* out, int dtype, int num_tiles, int H, int G, int M, int D, int E,
                                       int page_size, long long page_stride, int max_pages, float scale, float lambda, float post,
-                                      float eps, float out_scale, int TQ, int KT, long long out_ld, cudaStream_t stream) {
+                                      float eps, float out_scale, int TQ, int KT, long long out_ld, int window, int chunk, float softcap,
+                                      cudaStream_t stream) {
     if (out_ld < (long long)H * E) return forge::fail(FORGE_ERR_ARG, "scored_attention: output rows of %lld are too short", out_ld);
     if (num_tiles < 0 || H <= 0 || G <= 0 || D <= 0 || E <= 0 || H % G != 0 || (M != 1 && M != 2) || page_size <= 0 || max_pages <= 0 ||
         TQ <= 0 || KT <= 0)
@@ -276,6 +290,7 @@ extern "C" int forge_scored_attention(const void* q, const void* cache, const in
                            H, G, M, D, E, page_size, TQ, KT);
     if ((tile_t0 == nullptr) != (tile_n == nullptr)) return forge::fail(FORGE_ERR_ARG, "scored_attention: half a tile list");
     if ((r1 == nullptr) != (r2 == nullptr)) return forge::fail(FORGE_ERR_ARG, "scored_attention: r1 and r2 go together");
+    if (window < 0 || chunk < 0 || softcap < 0.f) return forge::fail(FORGE_ERR_ARG, "scored_attention: window %d, chunk %d, softcap %g", window, chunk, (double)softcap);
     if (num_tiles == 0) return FORGE_OK;
     const size_t smem = scored_smem_bytes(H / G, M, D, E, TQ, KT);
     if (smem > 200 * 1024)
@@ -290,7 +305,7 @@ extern "C" int forge_scored_attention(const void* q, const void* cache, const in
         }
         e = forge::launch(scored_attention_kernel<TT>, dim3(num_tiles, G), dim3(kAttThreads), smem, stream, 1, (const TT*)q,
                           (const TT*)cache, block_table, tok_req, positions, tile_t0, tile_n, r1, r2, (TT*)out, H, G, M, D, E, page_size,
-                          page_stride, max_pages, scale, lambda, post, eps, out_scale, TQ, KT, out_ld);
+                          page_stride, max_pages, scale, lambda, post, eps, out_scale, TQ, KT, out_ld, window, chunk, softcap);
     });
     return forge::check_launch("scored_attention", e);
 }

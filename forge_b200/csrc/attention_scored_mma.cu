@@ -17,6 +17,14 @@ namespace {
 constexpr int BM = 64, BN = 64, kThreads = 128, kPad = 8;
 constexpr int kMmaSmemLimit = 200 * 1024;
 
+// The first position that position `pos` sees (window: i - j < window; chunk: the same chunk of positions; 0 = no such limit).
+__device__ __forceinline__ int first_visible(int pos, int window, int chunk) {
+    int lo = 0;
+    if (window > 0) lo = max(lo, pos - window + 1);
+    if (chunk > 0) lo = max(lo, pos / chunk * chunk);
+    return lo;
+}
+
 __device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], const void* p) {
     const uint32_t a = (uint32_t)__cvta_generic_to_shared(p);
     asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];" : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(a));
@@ -57,7 +65,7 @@ scored_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __re
                   const int32_t* __restrict__ tok_req, const int32_t* __restrict__ positions, const int32_t* __restrict__ tile_t0,
                   const int32_t* __restrict__ tile_n, const float* __restrict__ r1, const float* __restrict__ r2, float* __restrict__ u,
                   __nv_bfloat16* __restrict__ out, float* __restrict__ part_ml, int nsplit_given, int T, int qrows, int H, int G, int M, int D, int E, int page_size, long long page_stride,
-                  int max_pages, float scale, float out_scale, long long out_ld) {
+                  int max_pages, float scale, float out_scale, long long out_ld, int window, int chunk, float softcap) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
     forge::pdl_launch_dependents();
     forge::pdl_wait();
@@ -100,6 +108,9 @@ scored_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __re
     const int r_lo = rb * 16 + (lane >> 2), r_hi = r_lo + 8;             // this thread's two rows
     const int pos_lo = pos0 + min(r_lo, rows - 1) / Gq, pos_hi = pos0 + min(r_hi, rows - 1) / Gq;
     const bool live_lo = r_lo < rows, live_hi = r_hi < rows;
+    const int see_lo = first_visible(pos_lo, window, chunk), see_hi = first_visible(pos_hi, window, chunk);
+    const int see_last = first_visible(pos_last, window, chunk);          // the tile's last token sees no earlier key than any other
+    const float cap_in = softcap > 0.f ? scale / softcap : 0.f, cap_out = softcap * 1.4426950408889634f;
     const int h_lo = c * Gq + min(r_lo, rows - 1) % Gq, h_hi = c * Gq + min(r_hi, rows - 1) % Gq;
     const float r1v[2] = {r1 ? r1[h_lo] : 0.f, r1 ? r1[h_hi] : 0.f}, r2v[2] = {r1 ? r2[h_lo] : 0.f, r1 ? r2[h_hi] : 0.f};
 
@@ -136,7 +147,10 @@ scored_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __re
         }
         copies_commit();
     };
-    const int n_tiles = last_tile + 1, per = (n_tiles + nsplit - 1) / nsplit, kt_lo = sp * per, kt_hi = min(n_tiles, kt_lo + per);
+    // key tiles that no token of the tile sees are skipped: they would add exact zeros
+    const int first_tile = first_visible(pos0, window, chunk) / BN;
+    const int n_tiles = last_tile + 1 - first_tile, per = (n_tiles + nsplit - 1) / nsplit, kt_lo = first_tile + sp * per,
+              kt_hi = min(last_tile + 1, kt_lo + per);
     if (kt_lo < kt_hi) fetch(kt_lo, 0);
     for (int kt = kt_lo; kt < kt_hi; ++kt) {
         const int j0 = kt * BN;
@@ -165,9 +179,9 @@ scored_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __re
                 }
             }
             // scale, distance term, mask, and the tile's maximum per row.  A tile that every row of the CTA sees whole needs no mask.
-            const bool whole = rows == BM && j0 + BN - 1 <= pos0;
+            const bool whole = rows == BM && j0 + BN - 1 <= pos0 && j0 >= see_last;
             float tmax[2] = {-INFINITY, -INFINITY};
-            if (whole && !r1) {
+            if (whole && !r1 && softcap == 0.f) {
 #pragma unroll
                 for (int nt = 0; nt < BN / 8; ++nt) {
 #pragma unroll
@@ -184,10 +198,10 @@ scored_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __re
                         const int j = j0 + nt * 8 + (lane & 3) * 2 + (e & 1);
                         const int hi = e >> 1;
                         const int pos = hi ? pos_hi : pos_lo;
-                        const bool ok = (hi ? live_hi : live_lo) && j <= pos;
+                        const bool ok = (hi ? live_hi : live_lo) && j <= pos && j >= (hi ? see_hi : see_lo);
                         float s = -INFINITY;
                         if (ok) {
-                            s = sacc[nt][e] * sl2;
+                            s = softcap > 0.f ? cap_out * tanhf(sacc[nt][e] * cap_in) : sacc[nt][e] * sl2;
                             // r1 ln(1 + r2 d) in units of log2(e) is r1 log2(1 + r2 d); lg2.approx errs by 2^-22, far below
                             // the rounding of the bfloat16 operands of q . k
                             if (r1) s -= r1v[hi] * __log2f(fmaf(r2v[hi], (float)(pos - j), 1.0f));
@@ -355,7 +369,8 @@ template <int VC, bool SPLIT>
 int launch_scored(int which, dim3 grid, size_t smem, cudaStream_t stream, const __nv_bfloat16* q, const __nv_bfloat16* cache,
                   const int32_t* bt, const int32_t* tok_req, const int32_t* positions, const int32_t* t0, const int32_t* tn, const float* r1,
                   const float* r2, float* u, __nv_bfloat16* out, float* part_ml, int nsplit, int T, int qrows, int H, int G, int M, int D, int E,
-                  int page_size, long long page_stride, int max_pages, float scale, float out_scale, long long out_ld) {
+                  int page_size, long long page_stride, int max_pages, float scale, float out_scale, long long out_ld, int window, int chunk,
+                  float softcap) {
     bool& done = g_attr_done[which + (SPLIT ? 3 : 0)].current();
     if (!done) {
         cudaError_t e = cudaFuncSetAttribute(scored_mma_kernel<VC, SPLIT>, cudaFuncAttributeMaxDynamicSharedMemorySize, kMmaSmemLimit);
@@ -365,7 +380,7 @@ int launch_scored(int which, dim3 grid, size_t smem, cudaStream_t stream, const 
     return forge::check_launch("scored_attention_mma",
                                forge::launch(scored_mma_kernel<VC, SPLIT>, grid, dim3(kThreads), smem, stream, 1, q, cache, bt, tok_req, positions, t0,
                                              tn, r1, r2, u, out, part_ml, nsplit, T, qrows, H, G, M, D, E, page_size, page_stride, max_pages, scale,
-                                             out_scale, out_ld));
+                                             out_scale, out_ld, window, chunk, softcap));
 }
 
 }  // namespace
@@ -381,16 +396,18 @@ extern "C" int forge_scored_mma_supports(int H, int G, int M, int D, int E, int 
 // [nsplit, T, H, M, 2] (scratch, nsplit > 1: steps of single tokens only); out bf16, rows of out_ld elements (even) with the
 // heads' H*E values at their start.  tile_t0 / tile_n: tiles of consecutive
 // tokens of one request with tile_n * (H/G) <= 64 (both null: one token per tile, num_tiles = T).  r1, r2 fp32 [H] or null.
+// window, chunk, softcap: the limits on what a position sees and the cap on the scores, 0 = none.
 extern "C" int forge_scored_attention_mma(const void* q, const void* cache, const int32_t* block_table, const int32_t* tok_req,
                                           const int32_t* positions, const int32_t* tile_t0, const int32_t* tile_n, const float* r1,
                                           const float* r2, float* u, float* part_ml, int nsplit, void* out, int T, int num_tiles, int H, int G, int M, int D, int E,
                                           int page_size, long long page_stride, int max_pages, float scale, float lambda, float post,
-                                          float eps, float out_scale, long long out_ld, cudaStream_t stream) {
+                                          float eps, float out_scale, long long out_ld, int window, int chunk, float softcap,
+                                          cudaStream_t stream) {
     if (out_ld < (long long)H * E || (out_ld & 1)) return forge::fail(FORGE_ERR_ARG, "scored_attention_mma: output rows of %lld elements", out_ld);
     if (!forge_scored_mma_supports(H, G, M, D, E, page_size))
         return forge::fail(FORGE_ERR_UNSUPPORTED, "scored_attention_mma: H=%d G=%d M=%d D=%d E=%d", H, G, M, D, E);
     if (T < 0 || num_tiles < 0 || max_pages <= 0 || (tile_t0 == nullptr) != (tile_n == nullptr) || (r1 == nullptr) != (r2 == nullptr) ||
-        ((M == 2 || nsplit > 1) && !u))
+        ((M == 2 || nsplit > 1) && !u) || window < 0 || chunk < 0 || softcap < 0.f)
         return forge::fail(FORGE_ERR_ARG, "scored_attention_mma: bad arguments");
     if (nsplit < 1 || nsplit > 16 || (nsplit > 1 && (tile_t0 != nullptr || part_ml == nullptr)))
         return forge::fail(FORGE_ERR_ARG, "scored_attention_mma: the keys are dealt out to several CTAs only in steps of single tokens");
@@ -408,7 +425,7 @@ extern "C" int forge_scored_attention_mma(const void* q, const void* cache, cons
     __nv_bfloat16* ob = (__nv_bfloat16*)out;
     const float os = (M == 1 && nsplit == 1) ? out_scale : 1.0f;
     int rc;
-#define FORGE_SCORED_ARGS grid, smem, stream, qb, cb, block_table, tok_req, positions, tile_t0, tile_n, r1, r2, u, ob, part_ml, nsplit, T, qrows, H, G, M, D, E, page_size, page_stride, max_pages, scale, os, out_ld
+#define FORGE_SCORED_ARGS grid, smem, stream, qb, cb, block_table, tok_req, positions, tile_t0, tile_n, r1, r2, u, ob, part_ml, nsplit, T, qrows, H, G, M, D, E, page_size, page_stride, max_pages, scale, os, out_ld, window, chunk, softcap
     if (nsplit > 1) rc = VC == 64 ? launch_scored<64, true>(0, FORGE_SCORED_ARGS) : VC == 128 ? launch_scored<128, true>(1, FORGE_SCORED_ARGS) : launch_scored<256, true>(2, FORGE_SCORED_ARGS);
     else rc = VC == 64 ? launch_scored<64, false>(0, FORGE_SCORED_ARGS) : VC == 128 ? launch_scored<128, false>(1, FORGE_SCORED_ARGS) : launch_scored<256, false>(2, FORGE_SCORED_ARGS);
 #undef FORGE_SCORED_ARGS

@@ -1,7 +1,10 @@
 // A feed-forward made of many small gated feed-forwards ("experts") of which a router picks a few per token.
 //
 //   route       z = Wr x in fp32, score = sigmoid(z) (or softmax over the experts), the `top` largest scores (the lower index
-//               wins a tie) are the token's experts and, as they are or divided by their sum, its weights
+//               wins a tie) are the token's experts and, as they are or divided by their sum, its weights.  Options: the choice
+//               is made by score + correction_e (the weights stay the scores); the experts form `groups` equal groups of
+//               neighbours, a group counts as its largest choice score, and only experts of the `keep` best groups can be
+//               chosen; the weights are multiplied by a factor
 //   by pairs    every (token, chosen expert) pair on its own: act = act_fn(Wg_e x) * (Wu_e x), then for every token
 //               y = sum over its experts, in the order the router chose them, of weight * Wd_e act.  Everything is read from
 //               device memory, so the path can be replayed in a CUDA graph; it is the path of steps with few tokens
@@ -54,7 +57,7 @@ constexpr int kRouteThreads = 256;
 template <typename TA>
 __global__ void __launch_bounds__(kRouteThreads)
 moe_route_kernel(const TA* __restrict__ x, const float* __restrict__ Wr, int32_t* __restrict__ idx, float* __restrict__ wts, int T,
-                 int W, int E, int top, int softmax, int renorm) {
+                 int W, int E, int top, int softmax, int renorm, const float* __restrict__ corr, int groups, int keep, float factor) {
     extern __shared__ float sc[];
     forge::pdl_launch_dependents();
     forge::pdl_wait();
@@ -75,19 +78,48 @@ moe_route_kernel(const TA* __restrict__ x, const float* __restrict__ Wr, int32_t
         } else {
             for (int e = 0; e < E; ++e) s[e] = sigmoidf(s[e]);
         }
+        // ch: what the choice is made by (the scores themselves unless a correction or groups say otherwise)
+        float* ch = s;
+        if (corr != nullptr || groups > 1) {
+            ch = s + E;
+            for (int e = 0; e < E; ++e) ch[e] = corr ? s[e] + corr[e] : s[e];
+        }
+        if (groups > 1) {
+            float* gs = ch + E;                      // a group's score: its largest choice score
+            const int per = E / groups;
+            for (int g = 0; g < groups; ++g) {
+                float b = -INFINITY;
+                for (int e = g * per; e < (g + 1) * per; ++e) b = fmaxf(b, ch[e]);
+                gs[g] = b;
+            }
+            // the `keep` best groups stay (the lower index wins a tie); a kept group is marked by NaN, which no comparison picks again
+            for (int k = 0; k < keep; ++k) {
+                int best = -1;
+                float bv = -INFINITY;
+                for (int g = 0; g < groups; ++g)
+                    if (gs[g] == gs[g] && (best < 0 || gs[g] > bv)) { bv = gs[g]; best = g; }
+                if (best >= 0) gs[best] = __int_as_float(0x7fc00000);
+            }
+            for (int g = 0; g < groups; ++g)
+                if (gs[g] == gs[g])
+                    for (int e = g * per; e < (g + 1) * per; ++e) ch[e] = -INFINITY;
+        }
         float total = 0.f;
         for (int k = 0; k < top; ++k) {
             int best = 0;
             float bv = -INFINITY;
             for (int e = 0; e < E; ++e)
-                if (s[e] > bv) { bv = s[e]; best = e; }
+                if (ch[e] > bv) { bv = ch[e]; best = e; }
             idx[(size_t)t * top + k] = best;
-            wts[(size_t)t * top + k] = bv;
-            total += bv;
-            s[best] = -INFINITY;
+            wts[(size_t)t * top + k] = s[best];
+            total += s[best];
+            ch[best] = -INFINITY;
         }
-        if (renorm)
-            for (int k = 0; k < top; ++k) wts[(size_t)t * top + k] /= total;
+        for (int k = 0; k < top; ++k) {
+            float w = wts[(size_t)t * top + k];
+            if (renorm) w /= total;
+            wts[(size_t)t * top + k] = w * factor;
+        }
     }
 }
 
@@ -433,15 +465,18 @@ moe_combine_kernel(const float* __restrict__ ys, const int32_t* __restrict__ des
 }  // namespace
 
 // x [T, W] of type dtype; Wr fp32 [E, W]; idx int32 [T, top]; wts fp32 [T, top].  softmax 0: scores are sigmoids.
+// corr fp32 [E] or null; groups <= 1: no groups, else E % groups == 0 and 1 <= keep <= groups with top <= keep * E / groups.
 extern "C" int forge_moe_route(const void* x, int dtype, const float* Wr, int32_t* idx, float* wts, int T, int W, int E, int top,
-                               int softmax, int renorm, cudaStream_t stream) {
+                               int softmax, int renorm, const float* corr, int groups, int keep, float factor, cudaStream_t stream) {
     if (T < 0 || W <= 0 || E <= 0 || top <= 0 || top > E) return forge::fail(FORGE_ERR_ARG, "moe_route: bad sizes T=%d W=%d E=%d top=%d", T, W, E, top);
+    if (groups > 1 && (E % groups != 0 || keep < 1 || keep > groups || top > keep * (E / groups)))
+        return forge::fail(FORGE_ERR_ARG, "moe_route: %d experts in %d groups of which %d are kept, %d experts a token", E, groups, keep, top);
     if (E > 2048) return forge::fail(FORGE_ERR_UNSUPPORTED, "moe_route: %d experts", E);
     if (T == 0) return FORGE_OK;
     cudaError_t e = cudaSuccess;
     FORGE_DISPATCH_DTYPE(dtype, TT,
-        e = forge::launch(moe_route_kernel<TT>, dim3(T), dim3(kRouteThreads), sizeof(float) * E, stream, 1, (const TT*)x, Wr, idx, wts, T, W,
-                          E, top, softmax, renorm));
+        e = forge::launch(moe_route_kernel<TT>, dim3(T), dim3(kRouteThreads), sizeof(float) * (2 * E + (groups > 1 ? groups : 0)), stream, 1, (const TT*)x, Wr,
+                          idx, wts, T, W, E, top, softmax, renorm, corr, groups > 1 ? groups : 0, keep, factor));
     return forge::check_launch("moe_route", e);
 }
 

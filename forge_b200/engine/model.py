@@ -35,6 +35,11 @@ class Model:
                 raise ConfigError(f"layer {i}: cache_from {spec.cache_from} is not a layer")
         if getattr(self.embedding, "needs_batch", False) and plan.add_embedding_before:
             raise ConfigError("an embedding that keeps state cannot be added to the stream again within a step")
+        if plan.streams != 1:
+            from ..parts.norm import RMSNorm
+            if plan.streams < 1 or plan.add_embedding_before or type(self.final_norm) is not RMSNorm:
+                raise ConfigError("a stream kept as several copies needs an RMS norm at the end and no embedding added on the way")
+            self._ones = None
         self.loaded = False
         self._fused = None
         self._replay_ok, self._replay_from, self._replay_tensors = False, 0, []
@@ -71,6 +76,8 @@ class Model:
             else:
                 part.bind(mine)
         self.loaded = True
+        if self.plan.streams != 1:
+            self._ones = torch.ones(self.plan.streams, dtype=torch.float32, device=self.rt.device)
         # layers whose launches may be repeated from one noted layer: all runs of the schedule from the first on, or
         # (a model whose first layer is of another kind) from the second on, declare it with one key
         runs = [replay_of(self.blocks[i]) for i in self.plan.schedule]
@@ -123,7 +130,8 @@ class Model:
         from .. import kernels
         self._fused = None
         sched = self.plan.schedule
-        if self.rt.full_precision or not sched or sched != list(range(len(self.blocks))) or self.plan.add_embedding_before:
+        if self.rt.full_precision or not sched or sched != list(range(len(self.blocks))) or self.plan.add_embedding_before \
+                or self.plan.streams != 1:
             return False
         descs = [b.fused_decode() if hasattr(b, "fused_decode") else None for b in self.blocks]
         if any(d is None for d in descs):
@@ -177,6 +185,9 @@ class Model:
             residual = self.embedding.forward_step(batch, embedding_cache)
         else:
             residual = self.embedding.forward(batch.token_ids, status=batch.status)
+        S = self.plan.streams
+        if S != 1:
+            residual = kernels.streams_expand(residual, S)          # every copy of the stream starts as the embedding output
         if self._fused_decode_applies(batch):
             fused, group = self._fused
             g = batch.groups[group]
@@ -211,7 +222,12 @@ class Model:
                     ws.release(m)              # a layer's intermediates are dead: the residual stream carries on
         if batch.num_logits == 0:
             return None
-        x = self.final_norm.forward(residual, rows=batch.logits_rows)
+        if S != 1:
+            # the last norm reads the sum of the copies
+            x = kernels.streams_mix(residual, S, in_next=self._ones, w_next=self.final_norm.weight, eps=self.final_norm.eps,
+                                    out_dtype=self.rt.dtype, rows=batch.logits_rows)
+        else:
+            x = self.final_norm.forward(residual, rows=batch.logits_rows)
         if workspace is None:
             return self.lm_head.forward(x)
         with workspace.paused():               # the logits are the caller's to keep

@@ -87,10 +87,10 @@ class ModelRunner:
                                     self.device, embedding_spec=self.model.embedding_cache_spec())
         self.manager = self.storage.manager
         # width of a request's block table.  A group that keeps every key can never give a request more
-        # pages than its pool has; a windowed group hands old pages back but its table keeps its logical
+        # pages than its pool has; a windowed (or chunked) group hands old pages back but its table keeps its logical
         # length (-1 where a page went), so it must reach the model's last position.
         self.max_pages_per_request = -(-self.plan.max_positions // self.page_size)
-        if all(g.window is None for g in self.manager.groups.values()):
+        if all(g.window is None and g.chunk is None for g in self.manager.groups.values()):
             self.max_pages_per_request = min(self.num_pages, self.max_pages_per_request)
         self.max_tokens_per_step = None if max_tokens_per_step is None else int(max_tokens_per_step)
         # Decode steps of up to 16 requests can run all their layers in ONE persistent kernel (csrc/decode_layers.cu).

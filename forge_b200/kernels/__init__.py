@@ -35,6 +35,8 @@ _SIGNATURES = {
         "forge_embedding": [_P, _P, _I, _P, _I, _I, _I, _F, _I, _P, _P],
         "forge_embedding_pair": [_P, _P, _P, _P, _P, _P, _LL, _P, _P, _I, _P, _I, _I, _I, _I, _LL, _LL, _P, _P],
         "forge_rmsnorm_add": [_P, _P, _P, _P, _P, _I, _I, _I, _F, _F, _P],
+        "forge_streams_expand": [_P, _P, _I, _I, _I, _P],
+        "forge_streams_mix": [_P] * 7 + [_I, _P, _I, _I, _I, _F, _P],
         "forge_layernorm": [_P, _P, _P, _P, _I, _P, _I, _I, _F, _P],
         "forge_act_rows": [_P, _I, _P, _I, _I, _I, _I, _P],
         "forge_rmsnorm": [_P, _P, _P, _I, _P, _I, _I, _F, _P],
@@ -70,9 +72,9 @@ _SIGNATURES = {
         "forge_headmix_attention_mma": [_P] * 11 + [_I, _P] + [_I] * 7 + [_LL, _I, _I, _I, _F, _P],
         "forge_state_scan": [_I, _P, _I, _P, _I, _P, _I, _P, _I, _P, _I, _P, _P, _P, _P, _P, _LL, _P, _P, _P, _P, _I, _I, _LL, _I, _I, _I, _I, _I, _P],
         "forge_scored_prepare": [_P, _I] + [_P] * 7 + [_I] * 8 + [_F, _F, _F, _I, _LL, _P],
-        "forge_scored_attention": [_P] * 10 + [_I] * 8 + [_LL, _I] + [_F] * 5 + [_I, _I, _LL, _P],
+        "forge_scored_attention": [_P] * 10 + [_I] * 8 + [_LL, _I] + [_F] * 5 + [_I, _I, _LL, _I, _I, _F, _P],
         "forge_scored_mma_supports": [_I] * 6,
-        "forge_scored_attention_mma": [_P] * 11 + [_I, _P] + [_I] * 8 + [_LL, _I] + [_F] * 5 + [_LL, _P],
+        "forge_scored_attention_mma": [_P] * 11 + [_I, _P] + [_I] * 8 + [_LL, _I] + [_F] * 5 + [_LL, _I, _I, _F, _P],
         "forge_token_shift": [_P, _P, _LL, _LL, _P, _P, _P, _P, _P, _I, _I, _I, _I, _P],
         "forge_head_finish": [_P, _P, _P, _I, _P, _I, _I, _I, _I, _F, _I, _F, _I, _LL, _P],
         "forge_tanh_rows": [_P, _I, _P, _I, _I, _I, _P],
@@ -80,14 +82,14 @@ _SIGNATURES = {
     },
     "latent": {
         "forge_latent_prepare": [_P, _I, _P, _P, _P, _F, _P, _P, _P, _P, _I, _I, _I, _I, _I, _F, _P],
-        "forge_head_linear": [_P, _I, _LL, _I, _P, _P, _I, _LL, _I, _P, _P, _F, _I, _I, _I, _I, _I, _I, _P],
-        "forge_latent_attention": [_P] * 8 + [_I] * 8 + [_F, _I, _I, _P],
+        "forge_head_linear": [_P, _I, _LL, _I, _P, _P, _I, _LL, _I, _P, _P, _F, _I, _I, _I, _I, _I, _I, _P, _LL, _P],
+        "forge_latent_attention": [_P] * 8 + [_I] * 8 + [_F, _I, _I, _I, _P, _P],
         "forge_latent_mma_supports": [_I] * 4,
         "forge_latent_mma_heads": [_I],
-        "forge_latent_attention_mma": [_P] * 9 + [_I, _P] + [_I] * 7 + [_F, _P],
+        "forge_latent_attention_mma": [_P] * 9 + [_I, _P] + [_I] * 7 + [_F, _I, _P, _P],
     },
     "moe": {
-        "forge_moe_route": [_P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _P],
+        "forge_moe_route": [_P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _P, _I, _I, _F, _P],
         "forge_moe_pair_gate_up": [_P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _LL, _P],
         "forge_moe_pair_down": [_P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _P],
         "forge_moe_expert_supports": [_I, _I, _I],
@@ -578,6 +580,38 @@ def rmsnorm_add(y, w_y, residual, eps, mult=1.0, w_next=None, out_dtype=None):
     return out
 
 
+def streams_expand(x, S):
+    """fp32 [T, W] -> fp32 [T, S*W]: S copies of every row side by side (a residual stream kept as S copies starts from the
+    embedding output in all of them)."""
+    lib = library("core")
+    T, W = x.shape
+    out = new_tensor((T, S * W), torch.float32, x.device)
+    _check(lib, lib.forge_streams_expand(_need(x, "x", torch.float32, 2), _need(out, "out", torch.float32), T, int(S), W, _stream()), "streams_expand")
+    return out
+
+
+def streams_mix(xs, S, y=None, mix=None, out_w=None, in_next=None, w_next=None, eps=0.0, out_dtype=None, rows=None):
+    """xs fp32 [T, S*W], the S copies of the stream.  With ``y`` fp32 [T, W] (a sublayer's output) every copy is rewritten at once
+    from the old ones, copy t <- sum_s mix[s, t] copy_s + out_w[t] y (mix fp32 [S, S], out_w fp32 [S]).  With ``in_next`` fp32 [S]
+    and ``w_next`` fp32 [W] returns rmsnorm(sum_s in_next[s] copy_s) * w_next of the (new) copies in ``out_dtype``, else None.
+    ``rows`` int32 [R] (reading only): the tokens whose rows are wanted."""
+    lib = library("core")
+    T, SW = xs.shape
+    W = SW // S
+    if S * W != SW or (y is not None and tuple(y.shape) != (T, W)):
+        raise KernelError(f"streams_mix: {tuple(xs.shape)} is not {S} copies of rows like y's {None if y is None else tuple(y.shape)}")
+    if (mix is not None and mix.numel() != S * S) or (out_w is not None and out_w.numel() != S) or (in_next is not None and in_next.numel() != S) \
+            or (w_next is not None and w_next.numel() != W):
+        raise KernelError("streams_mix: weights of the wrong size")
+    R = T if rows is None else rows.numel()
+    out = new_tensor((R, W), out_dtype, xs.device) if in_next is not None else None
+    _check(lib, lib.forge_streams_mix(
+        _need(xs, "xs", torch.float32, 2), _opt(y, "y", torch.float32), _opt(mix, "mix", torch.float32), _opt(out_w, "out_w", torch.float32),
+        _opt(in_next, "in_next", torch.float32), _opt(w_next, "w_next", torch.float32), _opt(out, "out", out_dtype),
+        dtype_code(out_dtype) if out is not None else F32, _opt(rows, "rows", torch.int32), R, int(S), W, float(eps), _stream()), "streams_mix")
+    return out
+
+
 def rmsnorm(x, weight, eps, out_dtype, rows=None, out=None):
     """y = x * rsqrt(mean(x^2)+eps) * w over the last dim of float32 x [T,H]; ``rows`` (int32) picks rows."""
     lib = library("core")
@@ -943,12 +977,15 @@ def scored_prepare(proj, positions, slot_mapping, cache, H, G, M, D, E, page_siz
 
 
 def scored_attention(q, cache, group_batch, batch, H, G, M, D, E, page_size, scale, r1=None, r2=None, lam=0.0, post=1.0, eps=0.0,
-                     out_scale=1.0, out=None):
+                     out_scale=1.0, out=None, window=0, chunk=0, softcap=0.0):
     """Causal softmax attention of every token of the step over its request's pages, M maps per head (see
     csrc/attention_scored.cu): scores scale q.k - r1_h ln(1 + r2_h (i - j)); with M = 2 the maps' outputs are combined as
     a1 - lam a2, divided by their root mean square (``eps`` inside the root) and multiplied by ``post``.  Returns [T, H*E] in
-    q's type, times ``out_scale``; ``out`` = (matrix, first column): written there instead (the matrix is returned)."""
+    q's type, times ``out_scale``; ``out`` = (matrix, first column): written there instead (the matrix is returned).
+    ``window``: position i sees j only if i - j < window; ``chunk``: only if floor(i / chunk) = floor(j / chunk); ``softcap``: scores
+    become softcap tanh(score / softcap); 0 switches each off."""
     lib = library("mixers")
+    window, chunk, softcap = int(window or 0), int(chunk or 0), float(softcap or 0.0)
     T = q.shape[0]
     out, out_ptr, out_ld = _out_slice(out, H * E, T, q.dtype, q.device)
     if q.dtype == torch.bfloat16 and _TENSOR_CORE_ATTENTION and lib.forge_scored_mma_supports.fn(H, G, M, D, E, page_size):
@@ -959,7 +996,8 @@ def scored_attention(q, cache, group_batch, batch, H, G, M, D, E, page_size, sca
             # a step of single tokens brings T * G * M * (value chunks) CTAs: deal a request's key tiles out to several, up to one
             # CTA per SM, as far as the longest context (the graph's bucket) has tiles
             ctas = T * G * M * -(-E // 256)
-            nsplit = max(1, min(8, -(-batch.max_context // 64), _sm_count(q.device) // max(1, ctas)))
+            reach = min([batch.max_context] + [n + 63 for n in (window, chunk) if n])      # a window may start inside a tile
+            nsplit = max(1, min(8, -(-reach // 64), _sm_count(q.device) // max(1, ctas)))
         u = new_tensor((nsplit, T, H, M, E), torch.float32, q.device) if (M == 2 or nsplit > 1) else None
         part_ml = new_tensor((nsplit, T, H, M, 2), torch.float32, q.device) if nsplit > 1 else None
         _check(lib, lib.forge_scored_attention_mma(
@@ -967,7 +1005,7 @@ def scored_attention(q, cache, group_batch, batch, H, G, M, D, E, page_size, sca
             _need(batch.tok_req, "tok_req", torch.int32), _need(batch.positions, "positions", torch.int32), _opt(t0, "tile_t0", torch.int32),
             _opt(tn, "tile_n", torch.int32), _opt(r1, "r1", torch.float32), _opt(r2, "r2", torch.float32), _opt(u, "u", torch.float32),
             _opt(part_ml, "part_ml", torch.float32), nsplit, out_ptr, T, tiles, H, G, M, D, E, page_size, _page_stride(cache), group_batch.block_table.shape[1],
-            float(scale), float(lam), float(post), float(eps), float(out_scale), out_ld, _stream()), "scored_attention_mma")
+            float(scale), float(lam), float(post), float(eps), float(out_scale), out_ld, window, chunk, softcap, _stream()), "scored_attention_mma")
         if M == 2 or nsplit > 1:
             count_launches(1)      # the kernel that puts the runs of key tiles, and the two maps, together
         return out
@@ -981,7 +1019,7 @@ def scored_attention(q, cache, group_batch, batch, H, G, M, D, E, page_size, sca
         _need(batch.tok_req, "tok_req", torch.int32), _need(batch.positions, "positions", torch.int32), _opt(t0, "tile_t0", torch.int32),
         _opt(tn, "tile_n", torch.int32), _opt(r1, "r1", torch.float32), _opt(r2, "r2", torch.float32), out_ptr,
         dtype_code(q.dtype), tiles, H, G, M, D, E, page_size, _page_stride(cache), group_batch.block_table.shape[1], float(scale),
-        float(lam), float(post), float(eps), float(out_scale), TQ, SCORED_KEYS_PER_CHUNK, out_ld, _stream()), "scored_attention")
+        float(lam), float(post), float(eps), float(out_scale), TQ, SCORED_KEYS_PER_CHUNK, out_ld, window, chunk, softcap, _stream()), "scored_attention")
     return out
 
 
@@ -1062,12 +1100,16 @@ def latent_prepare(proj, batch, slot_mapping, cache, freq, amp, wq, wc, Cq, C, R
     return cq
 
 
-def head_linear(x, w, H, K, N, out_dtype, R=0, positions=None, freq=None, amp=1.0, simt=False):
+def head_linear(x, w, H, K, N, out_dtype, R=0, positions=None, freq=None, amp=1.0, simt=False, gate=None):
     """out[t, h, :N] = sum_k x[t, h, k] w[h, k, :] for the H heads of x [T, H*(K+R)] (fp32 or the weights' type); with R > 0 a head's
     last R channels are rotated by position * freq (channel 2i with 2i+1, cos and sin times ``amp``) and follow the N outputs.
     w [H, K, N] in ``out_dtype``; returns [T, H*(N+R)] in ``out_dtype``.  bfloat16 weights go to the tensor cores (an fp32 x rounded to
-    bfloat16 on the way) unless ``simt`` asks for fp32 multiply-adds on the inputs as they are."""
+    bfloat16 on the way) unless ``simt`` asks for fp32 multiply-adds on the inputs as they are.  ``gate`` = (fp32 matrix, first
+    column): the outputs are multiplied by the sigmoid of the H*N numbers from that column of the token's row."""
     lib = library("latent")
+    gate_ptr, gate_ld = (None, 0) if gate is None else _cols(gate[0], gate[1])
+    if gate is not None and (R or gate[0].shape[0] != x.shape[0] or gate[0].shape[1] < gate[1] + H * N):
+        raise KernelError("head_linear: a gate wants rows of the step's tokens with H*N columns, and no rotated channels")
     T = x.shape[0]
     if x.shape[1] != H * (K + R) or tuple(w.shape) != (H, K, N) or w.dtype != out_dtype:
         raise KernelError(f"head_linear: x {tuple(x.shape)}, w {tuple(w.shape)} {w.dtype} do not fit {H} heads of {K}+{R} -> {N}")
@@ -1075,7 +1117,7 @@ def head_linear(x, w, H, K, N, out_dtype, R=0, positions=None, freq=None, amp=1.
     _check(lib, lib.forge_head_linear(
         _need(x, "x", ndim=2), dtype_code(x.dtype), H * (K + R), K + R, _need(w, "w"), _need(out, "out", out_dtype), dtype_code(out_dtype),
         H * (N + R), N + R, _opt(positions, "positions", torch.int32), _opt(freq, "freq", torch.float32), float(amp), T, H, K, N, R,
-        1 if simt else 0, _stream()), "head_linear")
+        1 if simt else 0, gate_ptr, gate_ld, _stream()), "head_linear")
     return out
 
 
@@ -1096,10 +1138,15 @@ def latent_tile_shape(H, C, R, single_tokens=False):
     return best
 
 
-def latent_attention(q, cache, group_batch, batch, H, C, R, page_size, scale):
+def latent_attention(q, cache, group_batch, batch, H, C, R, page_size, scale, window=0, sink=None):
     """Causal softmax attention of every token's H absorbed queries (q [T, H*(C+R)]) over its request's latent rows in
-    ``cache`` (rows of C + R; the values are a row's first C channels); returns the weighted latents [T, H*C] in q's type."""
+    ``cache`` (rows of C + R; the values are a row's first C channels); returns the weighted latents [T, H*C] in q's type.
+    ``window``: a position sees itself and the window - 1 positions before it (0: all); ``sink`` fp32 [H]: exp(sink_h) joins the
+    softmax denominator of head h."""
     lib = library("latent")
+    window = int(window or 0)
+    if sink is not None and sink.numel() != H:
+        raise KernelError(f"latent_attention: {sink.numel()} sinks for {H} heads")
     T = q.shape[0]
     if cache.dtype != q.dtype:
         raise KernelError("latent_attention: q and cache dtypes differ")
@@ -1112,7 +1159,8 @@ def latent_attention(q, cache, group_batch, batch, H, C, R, page_size, scale):
             # a step of single tokens brings T * (head groups) * (value chunks) CTAs: deal a request's tiles out to several, up to
             # one CTA per SM, as far as the longest context (the graph's bucket) has tiles
             ctas = T * -(-H // HG) * -(-C // 256)
-            nsplit = max(1, min(8, -(-batch.max_context // 64), _sm_count(q.device) // max(1, ctas)))
+            reach = min(batch.max_context, window + 63) if window else batch.max_context
+            nsplit = max(1, min(8, -(-reach // 64), _sm_count(q.device) // max(1, ctas)))
         u = new_tensor((nsplit, T, H, C), torch.float32, q.device) if nsplit > 1 else None
         part_ml = new_tensor((nsplit, T, H, 2), torch.float32, q.device) if nsplit > 1 else None
         out = new_tensor((T, H * C), q.dtype, q.device)
@@ -1120,8 +1168,8 @@ def latent_attention(q, cache, group_batch, batch, H, C, R, page_size, scale):
             _need(q, "q", torch.bfloat16, 2), _need(cache, "cache", torch.bfloat16), _need(group_batch.block_table, "block_table", torch.int32, 2),
             _need(batch.tok_req, "tok_req", torch.int32), _need(batch.positions, "positions", torch.int32), _opt(t0, "tile_t0", torch.int32),
             _opt(tn, "tile_n", torch.int32), _opt(u, "u", torch.float32), _opt(part_ml, "part_ml", torch.float32), nsplit,
-            _need(out, "out", torch.bfloat16), T, tiles, H, C, R, page_size, group_batch.block_table.shape[1], float(scale), _stream()),
-            "latent_attention_mma")
+            _need(out, "out", torch.bfloat16), T, tiles, H, C, R, page_size, group_batch.block_table.shape[1], float(scale), window,
+            _opt(sink, "sink", torch.float32), _stream()), "latent_attention_mma")
         if nsplit > 1:
             count_launches(1)      # the kernel that puts the runs of tiles together
         return out
@@ -1133,22 +1181,27 @@ def latent_attention(q, cache, group_batch, batch, H, C, R, page_size, scale):
         _need(q, "q", ndim=2), _need(cache, "cache"), _need(group_batch.block_table, "block_table", torch.int32, 2),
         _need(batch.tok_req, "tok_req", torch.int32), _need(batch.positions, "positions", torch.int32), _opt(t0, "tile_t0", torch.int32),
         _opt(tn, "tile_n", torch.int32), _need(out, "out", q.dtype), dtype_code(q.dtype), tiles, H, HG, C, R, page_size,
-        group_batch.block_table.shape[1], float(scale), TQ, LATENT_KEYS_PER_CHUNK, _stream()), "latent_attention")
+        group_batch.block_table.shape[1], float(scale), TQ, LATENT_KEYS_PER_CHUNK, window, _opt(sink, "sink", torch.float32), _stream()),
+        "latent_attention")
     return out
 
 
 # ---------------------------------------------------------------------------------------------- routed experts
 
-def moe_route(x, router, top, softmax=False, renorm=False):
+def moe_route(x, router, top, softmax=False, renorm=False, correction=None, groups=0, keep=0, factor=1.0):
     """(int32 [T, top] experts, fp32 [T, top] weights): the ``top`` largest of sigmoid (or softmax) of router . x per token, the lower
-    index winning a tie; the weights are those scores, divided by their sum with ``renorm``.  router fp32 [E, W]; fp32 arithmetic."""
+    index winning a tie; the weights are those scores, divided by their sum with ``renorm``, times ``factor``.  router fp32 [E, W];
+    fp32 arithmetic.  ``correction`` fp32 [E]: the choice is made by score + correction (the weights stay the scores).  ``groups``
+    > 1: the experts form that many equal groups of neighbours, a group counts as its largest choice score, and only experts of the
+    ``keep`` best groups can be chosen."""
     lib = library("moe")
     T, W = x.shape
     E = router.shape[0]
     idx = new_tensor((T, top), torch.int32, x.device)
     wts = new_tensor((T, top), torch.float32, x.device)
     _check(lib, lib.forge_moe_route(_need(x, "x", ndim=2), dtype_code(x.dtype), _need(router, "router", torch.float32, 2), _need(idx, "idx"),
-                                    _need(wts, "wts"), T, W, E, int(top), 1 if softmax else 0, 1 if renorm else 0, _stream()), "moe_route")
+                                    _need(wts, "wts"), T, W, E, int(top), 1 if softmax else 0, 1 if renorm else 0,
+                                    _opt(correction, "correction", torch.float32), int(groups or 0), int(keep or 0), float(factor), _stream()), "moe_route")
     return idx, wts
 
 

@@ -20,8 +20,9 @@ CSRC = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))),
 
 LIBRARIES = {
     # embedding, norm, rotary + cache write, activation, fp32 GEMM, fp32/any-shape attention, sampling
+    # ... and a residual stream kept as several copies
     "core": ["embedding.cu", "norm.cu", "rope_cache.cu", "activation.cu", "gemm_simt.cu",
-             "attention_simt.cu", "sampling.cu"],
+             "attention_simt.cu", "sampling.cu", "streams.cu"],
     # bf16 tcgen05 + TMA GEMM with fused epilogues
     "gemm_sm100": ["gemm_sm100.cu"],
     # bf16 tensor-core paged attention (mma.sync) for any head size, prompt portions and decode

@@ -44,12 +44,15 @@ class KVCacheSpec:
     ``window``: only the last ``window`` positions are ever read (None: all of them), and, with ``keep_first``, the first
     ``keep_first`` positions of the sequence, which are never given back.  ``v_head_dim``: size of a value head when
     it is not the key's; a page is then one row, [num_kv_heads, page_size, head_dim] keys followed by [num_kv_heads,
-    page_size, v_head_dim] values; 0: no values are kept (the mixer reads them out of the key rows)."""
+    page_size, v_head_dim] values; 0: no values are kept (the mixer reads them out of the key rows).  ``chunk``: a position reads
+    only the positions of its own chunk of that many (counted from the sequence's start), so whole chunks behind the sequence's
+    end are never read again."""
     num_kv_heads: int
     head_dim: int
     window: Optional[int] = None
     v_head_dim: Optional[int] = None
     keep_first: int = 0
+    chunk: Optional[int] = None
 
     @property
     def value_dim(self):

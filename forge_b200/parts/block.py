@@ -7,6 +7,10 @@ the epilogue of each part's last matrix product, in fp32.
 "sandwich":  r += m * norm_b(mixer(norm_a(r)));  r += m * norm_d(feed_forward(norm_c(r))): every sublayer's OUTPUT goes
 through an RMS norm of its own before it joins the stream, times a number m.  The output norm, the addition and the next
 sublayer's input norm are one kernel.
+"hyper_connections":  the stream is S copies x_1 .. x_S (all equal to the embedding output at the start; their sum is what the
+model's last norm reads).  Around sublayer q (1: mixer, 2: feed-forward), with weights in_q [S], out_q [S], mix_q [S, S]:
+    u = sum_s in_q[s] x_s;   y = sublayer(norm_q(u));   x_t <- sum_s mix_q[s, t] x_s + out_q[t] y   (all t at once, from the old copies)
+in place of the residual sum.  A sublayer's write and the next sublayer's read and norm are one kernel.
 """
 from ..weights.loader import TensorSpec  # noqa: F401  (re-exported for part authors)
 from .base import Part, build_part, register_part
@@ -184,6 +188,66 @@ class SandwichBlock(Part):
         kernels.rmsnorm_add(y, n["ff_out"].weight, residual, n["ff_out"].eps, self.mult)
 
 
+class HyperConnectionBlock(Part):
+    """``norms``: {"mixer_in", "ff_in"} (the second None in a layer without feed-forward), RMS norms; ``layer_spec.block_params``:
+    {"streams": S}.  ``residual`` is fp32 [T, S*W], a token's copies side by side.  Mixer and feed-forward are called without a
+    stream to add into and return their output.  Tensors: ``hc1.in``, ``hc1.out``, ``hc1.mix``, and ``hc2.*`` with a feed-forward."""
+    graph_safe = True
+
+    def sub_parts(self):
+        return [p for p in (self.mixer, self.feed_forward, *self.norms.values()) if p is not None]
+
+    def __init__(self, rt, layer_spec):
+        from ..config.base import ConfigError
+        from .norm import RMSNorm
+        self.rt = rt
+        self.streams = int((layer_spec.block_params or {}).get("streams", 1))
+        if self.streams < 1:
+            raise ConfigError(f"a stream of {self.streams} copies")
+        self.mixer = build_part("mixer", layer_spec.mixer, rt)
+        self.feed_forward = build_part("feed_forward", layer_spec.feed_forward, rt)
+        self.norms = {k: None if layer_spec.norms.get(k) is None else build_part("norm", layer_spec.norms[k], rt) for k in ("mixer_in", "ff_in")}
+        if self.norms["mixer_in"] is None or any(n is not None and type(n) is not RMSNorm for n in self.norms.values()):
+            raise ConfigError("a layer on a stream of several copies needs an RMS norm before its mixer (and one before its feed-forward)")
+        self.weights = {}
+
+    def _children(self):
+        return [p for p in (self.mixer, self.feed_forward, *self.norms.values()) if p is not None]
+
+    def _sublayers(self):
+        return (1, 2) if self.norms["ff_in"] is not None else (1,)
+
+    def tensor_specs(self):
+        S = self.streams
+        specs = {}
+        for part in self._children():
+            specs.update(part.tensor_specs())
+        for q in self._sublayers():
+            specs.update({f"hc{q}.in": TensorSpec((S,), role="stream_in"), f"hc{q}.out": TensorSpec((S,), role="stream_in"),
+                          f"hc{q}.mix": TensorSpec((S, S), role="head_mix")})
+        return specs
+
+    def bind(self, tensors):
+        for part in self._children():
+            part.bind({name: tensors[name] for name in part.tensor_specs() if name in tensors})
+        for q in self._sublayers():
+            for k in ("in", "out", "mix"):
+                self.weights[f"{q}.{k}"] = self._vector_f32(tensors[f"hc{q}.{k}"])
+
+    def forward(self, residual, batch, cache):
+        from .. import kernels
+        S, w, n1, n2 = self.streams, self.weights, self.norms["mixer_in"], self.norms["ff_in"]
+        x = kernels.streams_mix(residual, S, in_next=w["1.in"], w_next=n1.weight, eps=n1.eps, out_dtype=self.rt.dtype)
+        y = self.mixer.forward(x, batch, cache, None)
+        if n2 is None:
+            kernels.streams_mix(residual, S, y=y, mix=w["1.mix"], out_w=w["1.out"])
+            return
+        x = kernels.streams_mix(residual, S, y=y, mix=w["1.mix"], out_w=w["1.out"], in_next=w["2.in"], w_next=n2.weight, eps=n2.eps,
+                                out_dtype=self.rt.dtype)
+        y = self.feed_forward.forward(x, None)
+        kernels.streams_mix(residual, S, y=y, mix=w["2.mix"], out_w=w["2.out"])
+
+
 def build_block(layer_spec, rt):
     from .base import _REGISTRY
     from ..config.base import ConfigError
@@ -197,3 +261,4 @@ def build_block(layer_spec, rt):
 register_part("block", "pre_norm", PreNormBlock, replace=True)
 register_part("block", "parallel", ParallelBlock, replace=True)
 register_part("block", "sandwich", SandwichBlock, replace=True)
+register_part("block", "hyper_connections", HyperConnectionBlock, replace=True)

@@ -14,6 +14,11 @@ and values per head are never formed: one path for prompt portions and single to
 Wdkv: it reads the rows that the named layer wrote, with matrices of its own.
 
 The rotation pairs channel 2i with 2i+1; its frequencies (and the factor on cos and sin) come from the position part.
+
+Options, each a constructor parameter: ``window`` (position i sees j only if i - j < window; the rows behind every future query's
+window go back to the pool), ``sink`` (a number per head whose exponential joins the softmax denominator: it has no key and no
+value, is not scaled, and counts once), ``out_gate`` (the concatenated heads are multiplied by sigmoid(Wg h) before Wo; Wg rides
+in the down-projections' product).
 """
 import torch
 
@@ -28,13 +33,17 @@ class LatentAttention(Part):
     graph_safe = True       # positions, tables, slots and request boundaries are read from the batch's device tensors
 
     def __init__(self, rt, hidden_size, num_heads, head_dim, rot_dim, v_head_dim, kv_rank, q_rank, scale, eps, position,
-                 own_latent=True, prefix="mix."):
+                 own_latent=True, prefix="mix.", window=None, sink=False, out_gate=False):
         if rot_dim % 2:
             raise ConfigError(f"latent attention: the rotated part has {rot_dim} channels, an odd number")
         self.rt, self.hidden_size, self.num_heads = rt, hidden_size, num_heads
         self.head_dim, self.rot_dim, self.v_head_dim = head_dim, rot_dim, v_head_dim
         self.kv_rank, self.q_rank, self.scale, self.eps = kv_rank, q_rank, float(scale), float(eps)
         self.own_latent, self.prefix = bool(own_latent), prefix
+        self.window, self.sink, self.out_gate = (int(window) if window else None), bool(sink), bool(out_gate)
+        if self.window is not None and self.window < 1:
+            raise ConfigError(f"latent attention: a window of {window} positions")
+        self.sinks = None
         self.position = build_part("position", position, rt)
         if not hasattr(self.position, "inv_freq") or 2 * self.position.inv_freq.numel() != rot_dim:
             raise ConfigError("latent attention rotates inside its own kernels and needs a position part with 'inv_freq' over the "
@@ -53,12 +62,18 @@ class LatentAttention(Part):
                  self._n("o"): TensorSpec((W, H * E))}
         if self.own_latent:
             specs.update({self._n("dkv"): TensorSpec((C + R, W)), self._n("dkv.norm"): TensorSpec((C,), role="norm")})
+        if self.sink:
+            specs[self._n("sink")] = TensorSpec((H,), role="bias")
+        if self.out_gate:
+            specs[self._n("g")] = TensorSpec((H * E, W))
         return specs
 
     def bind(self, tensors):
         H, D, E, C = self.num_heads, self.head_dim, self.v_head_dim, self.kv_rank
-        down = [tensors[self._n("dq")]] + ([tensors[self._n("dkv")]] if self.own_latent else [])
-        self.down = Linear(self._matrix(torch.cat(down, dim=0)), None, self.rt)          # both down-projections: one product
+        down = [tensors[self._n("dq")]] + ([tensors[self._n("dkv")]] if self.own_latent else []) + \
+            ([tensors[self._n("g")]] if self.out_gate else [])
+        self.down = Linear(self._matrix(torch.cat(down, dim=0)), None, self.rt)          # the down-projections (and the gate): one product
+        self.sinks = self._vector_f32(tensors[self._n("sink")]) if self.sink else None
         self.wq = self._vector_f32(tensors[self._n("dq.norm")])
         self.wc = self._vector_f32(tensors[self._n("dkv.norm")]) if self.own_latent else None
         self.uq = Linear(self._matrix(tensors[self._n("uq")]), None, self.rt)
@@ -69,7 +84,7 @@ class LatentAttention(Part):
 
     def cache_spec(self):
         # one key/value head whose rows are [c | kr]; no separate values (they are a row's first C channels)
-        return KVCacheSpec(1, self.kv_rank + self.rot_dim, None, v_head_dim=0)
+        return KVCacheSpec(1, self.kv_rank + self.rot_dim, self.window, v_head_dim=0)
 
     def forward(self, x, batch, cache, residual):
         """Adds the mixer's output into ``residual``, or (``residual`` None) returns it as a new fp32 [T, W]."""
@@ -77,12 +92,14 @@ class LatentAttention(Part):
         g = batch.groups[cache.group]
         freq, amp = self.position.inv_freq, self.position.amplitude
         store = self.own_latent and cache.writable
-        cq = kernels.latent_prepare(self.down.forward(x), batch, g.slot_mapping if store else None, cache.kv if store else None, freq, amp,
+        proj = self.down.forward(x)                                                    # fp32 [T, Cq (+ C + R) (+ H*E)]
+        cq = kernels.latent_prepare(proj, batch, g.slot_mapping if store else None, cache.kv if store else None, freq, amp,
                                     self.wq, self.wc, Cq, C if self.own_latent else 0, R, self.eps, self.rt.dtype)
         q = self.uq.forward(cq)                                                        # fp32 [T, H*(D+R)]
         qa = kernels.head_linear(q, self.uk, H, D, C, self.rt.dtype, R=R, positions=batch.positions, freq=freq, amp=amp)
-        lat = kernels.latent_attention(qa, cache.kv, g, batch, H, C, R, cache.page_size, self.scale)
-        o = kernels.head_linear(lat, self.uv, H, C, E, self.rt.dtype)
+        lat = kernels.latent_attention(qa, cache.kv, g, batch, H, C, R, cache.page_size, self.scale, window=self.window or 0, sink=self.sinks)
+        gate = (proj, Cq + (C + R if self.own_latent else 0)) if self.out_gate else None
+        o = kernels.head_linear(lat, self.uv, H, C, E, self.rt.dtype, gate=gate)
         return self.o.forward(o, accumulate_into=residual)
 
 

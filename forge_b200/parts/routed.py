@@ -3,6 +3,10 @@
     s = sigmoid(Wr x)  (or softmax(Wr x));   the ``top`` largest s choose the experts (the lower index wins a tie)
     y = sum over the chosen e of s_e * Wdown_e (silu(Wgate_e x) * (Wup_e x))          (s_e divided by their sum with ``renormalize``)
 
+Options: the choice may be made by s + ``correction`` (a number per expert; the weights stay s); the experts may form ``groups``
+equal groups of neighbours of which only the ``keep`` with the largest choice score in them can be chosen from; the weights may be
+multiplied by ``route_scale``; a ``shared`` feed-forward (any feed-forward part) may run for every token and be added.
+
 The router's arithmetic is fp32.  Three paths, all with everything but the last one's row counts read from device memory:
 
   by pairs      fewer (token, expert) pairs than experts: each pair on its own streams its expert's rows once (32-bit runs: every
@@ -19,7 +23,7 @@ import torch
 from .. import kernels
 from ..config.base import ConfigError
 from ..weights.loader import TensorSpec
-from .base import Part, register_part
+from .base import Part, build_part, register_part
 from .linear import Linear
 
 
@@ -28,9 +32,17 @@ class RoutedExperts(Part):
     SORTED_FROM = 128          # tokens in a step from which the pairs are ranked by expert
     BY_EXPERT_FROM = 2         # ... and from which the path by pairs goes expert by expert (the same numbers, fewer reads)
 
-    def __init__(self, rt, hidden_size, intermediate_size, experts, top, score="sigmoid", renormalize=False, prefix="mlp."):
+    def __init__(self, rt, hidden_size, intermediate_size, experts, top, score="sigmoid", renormalize=False, prefix="mlp.",
+                 correction=False, groups=0, keep=0, route_scale=1.0, shared=None):
+        """``shared``: the PartSpec of a feed-forward part that every token passes through beside its experts, or None."""
         if not 1 <= top <= experts:
             raise ConfigError(f"routed feed-forward: {top} of {experts} experts")
+        groups, keep = int(groups or 0), int(keep or 0)
+        if groups > 1 and (experts % groups or not 1 <= keep <= groups or top > keep * (experts // groups)):
+            raise ConfigError(f"routed feed-forward: {experts} experts in {groups} groups of which {keep} are kept cannot give {top} a token")
+        self.correction, self.groups, self.keep, self.route_scale = bool(correction), groups if groups > 1 else 0, keep, float(route_scale)
+        self.shared = None if shared is None else build_part("feed_forward", shared, rt)
+        self.bias = None
         if score not in ("sigmoid", "softmax"):
             raise ConfigError(f"routed feed-forward: scores are 'sigmoid' or 'softmax', not {score!r}")
         self.rt, self.hidden_size, self.intermediate_size = rt, hidden_size, intermediate_size
@@ -46,11 +58,21 @@ class RoutedExperts(Part):
             specs.update({self._n(f"e{e}.gate"): TensorSpec((F, W)), self._n(f"e{e}.up"): TensorSpec((F, W)),
                           self._n(f"e{e}.down"): TensorSpec((W, F))})
         specs[self._n("router")] = TensorSpec((self.experts, W))
+        if self.correction:
+            specs[self._n("correction")] = TensorSpec((self.experts,), role="bias")
+        if self.shared is not None:
+            specs.update(self.shared.tensor_specs())
         return specs
+
+    def sub_parts(self):
+        return [] if self.shared is None else [self.shared]
 
     def bind(self, tensors):
         W, F, E = self.hidden_size, self.intermediate_size, self.experts
         self.router = self._vector_f32(tensors[self._n("router")])                     # fp32 whatever the runtime
+        self.bias = self._vector_f32(tensors[self._n("correction")]) if self.correction else None
+        if self.shared is not None:
+            self.shared.bind({n: tensors[n] for n in self.shared.tensor_specs()})
         # one tensor per kind for all experts; gate and up rows alternate so that the product's epilogue sees (gate, up) pairs
         gu = torch.stack([torch.stack([tensors[self._n(f"e{e}.gate")], tensors[self._n(f"e{e}.up")]], dim=1).reshape(2 * F, W)
                           for e in range(E)])
@@ -93,7 +115,8 @@ class RoutedExperts(Part):
 
     def forward(self, x, residual):
         """Adds the output into ``residual`` fp32 [T, W], or (``residual`` None) returns it as a new fp32 [T, W]."""
-        idx, wts = kernels.moe_route(x, self.router, self.top, softmax=self.score == "softmax", renorm=self.renormalize)
+        idx, wts = kernels.moe_route(x, self.router, self.top, softmax=self.score == "softmax", renorm=self.renormalize,
+                                     correction=self.bias, groups=self.groups, keep=self.keep, factor=self.route_scale)
         T = x.shape[0]
         tensor_core = self.gate_up_of[0].tensor_core and self.down_of[0].tensor_core
         if T >= self.SORTED_FROM and not torch.cuda.is_current_stream_capturing():
@@ -106,6 +129,8 @@ class RoutedExperts(Part):
             y = kernels.moe_experts(x, idx, wts, self.gate_up, self.down)
         else:
             y = kernels.moe_pairs(x, idx, wts, self.gate_up, self.down)
+        if self.shared is not None:
+            self.shared.forward(x, y)              # its last product adds into the experts' sum
         if residual is None:
             return y
         residual.add_(y)

@@ -1,4 +1,4 @@
-"""Two causal softmax attentions whose scores are shaped before the softmax, both on the paged cache and on the same
+"""Three causal softmax attentions whose scores are shaped before the softmax, all on the paged cache and on the same
 kernels (``kernels.scored_prepare`` / ``kernels.scored_attention``); query/key heads and value heads may differ in size.
 
 "differential_attention": every head has two maps (q and k carry two vectors of D channels per head, [map 1 | map 2]),
@@ -10,6 +10,11 @@ Rotary positions on the first ``rotary_dims`` channels of every map, channel i p
 "distance_attention": no rotation; biases in every projection; an RMS norm over ALL query channels of a token (and all
 key channels) with a weight per channel; a query temperature 1 + coef ln(floor((p + 1) / every) + 1) at position p; and
     score(i, j) = scale q(i) . k(j) - r1_h ln(1 + r2_h (i - j))
+
+"masked_attention": no rotation (positions do not enter the scores); optional biases in q, k and v; the scale is a parameter;
+optionally  score <- softcap tanh(score / softcap);  and a position i sees j <= i only
+    within a sliding ``window``  (i - j < window),  or  within its own ``chunk``  (floor(i / chunk) = floor(j / chunk)),
+chunks counted from the sequence's first position.  Pages whose keys no future query sees go back to the pool.
 
 ``out_scale`` multiplies the mixer's output (a mixer that runs beside another with weights of their own).
 """
@@ -43,6 +48,9 @@ class _ScoredAttention(Part):
 
     def cache_spec(self):
         return KVCacheSpec(self.num_kv_heads, self.MAPS * self.head_dim, None, v_head_dim=self.v_head_dim)
+
+    def sub_parts(self):
+        return []
 
     # A mixer that runs beside others may share their input and output products: it says how many columns of the fused
     # projection are its own and how many of the output product's input, and offers ``mix`` (everything between the two).
@@ -145,5 +153,52 @@ class DistanceBiasAttention(_ScoredAttention):
                                         out_scale=self.out_scale, out=out)
 
 
+class MaskedAttention(_ScoredAttention):
+    def __init__(self, rt, hidden_size, num_heads, num_kv_heads, head_dim, v_head_dim=None, scale=None, window=None, chunk=None,
+                 softcap=None, qkv_bias=False, out_scale=1.0, prefix="mix."):
+        """``window`` / ``chunk``: None or a number of positions (both may be given: a key must pass both); ``softcap``: None or the
+        cap; ``qkv_bias``: tensors ``q.b``, ``k.b``, ``v.b`` are added in the projection."""
+        self._sizes(rt, hidden_size, num_heads, num_kv_heads, head_dim, v_head_dim, scale, out_scale, prefix)
+        self.window, self.chunk = (int(window) if window else None), (int(chunk) if chunk else None)
+        self.softcap, self.qkv_bias = (float(softcap) if softcap else None), bool(qkv_bias)
+        if (self.window is not None and self.window < 1) or (self.chunk is not None and self.chunk < 1) or \
+                (self.softcap is not None and not self.softcap > 0.0):
+            raise ConfigError(f"masked attention: window {window}, chunk {chunk}, softcap {softcap}")
+
+    def tensor_specs(self):
+        W, H, G, D, E = self.hidden_size, self.num_heads, self.num_kv_heads, self.head_dim, self.v_head_dim
+        specs = {self._n("q"): TensorSpec((H * D, W)), self._n("k"): TensorSpec((G * D, W)), self._n("v"): TensorSpec((G * E, W)),
+                 self._n("o"): TensorSpec((W, H * E))}
+        if self.qkv_bias:
+            specs.update({self._n("q.b"): TensorSpec((H * D,), role="bias"), self._n("k.b"): TensorSpec((G * D,), role="bias"),
+                          self._n("v.b"): TensorSpec((G * E,), role="bias")})
+        return specs
+
+    def bind(self, tensors):
+        rows = torch.cat([tensors[self._n(m)] for m in "qkv"], dim=0)
+        b = self._vector_f32(torch.cat([tensors[self._n(m + ".b")].float() for m in "qkv"])) if self.qkv_bias else None
+        self.proj = Linear(self._matrix(rows), b, self.rt)              # q, k, v in one product, the biases in its epilogue
+        self.o = Linear(self._matrix(tensors[self._n("o")]), None, self.rt)
+
+    def cache_spec(self):
+        return KVCacheSpec(self.num_kv_heads, self.head_dim, self.window, v_head_dim=self.v_head_dim, chunk=self.chunk)
+
+    def forward(self, x, batch, cache, residual):
+        """Adds the mixer's output into ``residual``, or (``residual`` None) returns it as a new fp32 [T, W]."""
+        o = self.mix(self.proj.forward(x), 0, batch, cache)
+        return self.o.forward(o, accumulate_into=residual)
+
+    def mix(self, proj, col, batch, cache, out=None):
+        """proj fp32 [T, >= col + in_width]: [q | k | v] from column ``col``, biases added; returns the heads' outputs
+        [T, H*E] (or writes them into ``out`` = (matrix, first column))."""
+        H, G, D, E = self.num_heads, self.num_kv_heads, self.head_dim, self.v_head_dim
+        g = batch.groups[cache.group]
+        q = kernels.scored_prepare(proj, batch.positions, g.slot_mapping if cache.writable else None,
+                                   cache.kv if cache.writable else None, H, G, 1, D, E, cache.page_size, self.rt.dtype, col=col)
+        return kernels.scored_attention(q, cache.kv, g, batch, H, G, 1, D, E, cache.page_size, self.scale, out_scale=self.out_scale,
+                                        out=out, window=self.window or 0, chunk=self.chunk or 0, softcap=self.softcap or 0.0)
+
+
 register_part("mixer", "differential_attention", DifferentialAttention, replace=True)
+register_part("mixer", "masked_attention", MaskedAttention, replace=True)
 register_part("mixer", "distance_attention", DistanceBiasAttention, replace=True)
