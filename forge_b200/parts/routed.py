@@ -59,7 +59,7 @@ class RoutedExperts(Part):
                           self._n(f"e{e}.down"): TensorSpec((W, F))})
         specs[self._n("router")] = TensorSpec((self.experts, W))
         if self.correction:
-            specs[self._n("correction")] = TensorSpec((self.experts,), role="bias")
+            specs[self._n("correction")] = TensorSpec((self.experts,), role="route_bias")
         if self.shared is not None:
             specs.update(self.shared.tensor_specs())
         return specs

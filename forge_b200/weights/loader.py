@@ -38,7 +38,7 @@ class TensorSpec:
     required: bool = True
     integer: bool = False        # an integer table (kept int32) rather than floating-point weights
     # how random weights are drawn for it: "matrix" | "embedding" | "norm" | "bias" | "fraction" (uniform in 0..1) |
-    # "head_mix" (the unit matrix plus noise)
+    # "head_mix" (the unit matrix plus noise) | "stream_in" (numbers around 0.7) | "route_bias" (small numbers around 0) | ...
     role: str = "matrix"
     # a size of -1 in ``shape`` is given by the file alone (the part reads it when it binds); ``default_shape`` is what
     # random weights take for such a tensor

@@ -38,6 +38,8 @@ def random_tensors(config, seed=0, std=0.02, embed_std=None, norm_std=0.0, bias_
             out[name] = (t + torch.randn(spec.shape, generator=gen, dtype=torch.float32, device=device) * 0.3).to(dtype)
         elif spec.role == "stream_in":        # what a copy of the stream adds to a sublayer's input, or takes of its output
             out[name] = (0.7 + 0.3 * torch.randn(spec.shape, generator=gen, dtype=torch.float32, device=device)).to(dtype)
+        elif spec.role == "route_bias":       # what is added to a router's scores (of order 1 / experts) before the choice
+            out[name] = (0.05 * torch.randn(spec.shape, generator=gen, dtype=torch.float32, device=device)).to(dtype)
         elif spec.role == "lambda_part":      # vectors whose pairwise dot products are exponentiated: keep those of order 1/2
             n = max(1, int(torch.tensor(spec.shape).prod()))
             out[name] = (torch.randn(spec.shape, generator=gen, dtype=torch.float32, device=device) * (0.7 / n ** 0.25)).to(dtype)

@@ -114,20 +114,25 @@ def gated_ff(x, w_gate, w_up, w_down):
 
 
 def route(x, w, r):
-    """(chosen experts [T, top], their weights [T, top], the margin between the last chosen and the first not chosen)."""
+    """(chosen experts [T, top], their weights [T, top], margin [T]: how far the choice is from another one, the smaller of the
+    gap between the last chosen and the first not chosen choice score and the gap between the last kept and the first dropped group)."""
     s = torch.softmax(x @ w["router"].T, dim=-1)
     choice = s + w["correction"]
     n, groups = r["experts"], r.get("groups")
+    margin = torch.full((x.shape[0],), math.inf, dtype=x.dtype)
     if groups:
         per = n // groups["count"]
         best = choice.view(-1, groups["count"], per).max(dim=-1).values
-        kept = best.topk(groups["keep"], dim=-1).indices
-        allowed = torch.zeros_like(best, dtype=torch.bool).scatter_(1, kept, True)
+        ranked = best.sort(dim=-1, descending=True)
+        if groups["keep"] < groups["count"]:
+            margin = ranked.values[:, groups["keep"] - 1] - ranked.values[:, groups["keep"]]
+        allowed = torch.zeros_like(best, dtype=torch.bool).scatter_(1, ranked.indices[:, :groups["keep"]], True)
         choice = choice.masked_fill(~allowed.repeat_interleave(per, dim=1), -math.inf)
     ranked = choice.sort(dim=-1, descending=True)
     idx = ranked.indices[:, :r["top"]]
-    margin = ranked.values[:, r["top"] - 1] - ranked.values[:, r["top"]] if r["top"] < n else torch.full((x.shape[0],), math.inf)
-    return idx, s.gather(1, idx) * r["scale"], margin
+    if r["top"] < n:
+        margin = torch.minimum(margin, ranked.values[:, r["top"] - 1] - ranked.values[:, r["top"]])
+    return idx, s.gather(1, idx) * r.get("scale", 1.0), margin
 
 
 def routed_ff(x, w, mlp, chosen=None):
@@ -136,7 +141,7 @@ def routed_ff(x, w, mlp, chosen=None):
     idx, wts, margin = route(x, w, r)
     if chosen is not None:
         idx = chosen
-        wts = torch.softmax(x @ w["router"].T, dim=-1).gather(1, idx) * r["scale"]
+        wts = torch.softmax(x @ w["router"].T, dim=-1).gather(1, idx) * r.get("scale", 1.0)
     y = torch.zeros_like(x)
     for t in range(x.shape[0]):
         for k in range(idx.shape[1]):
@@ -182,25 +187,26 @@ def mixer(kind, h, w, m, eps):
 
 def forward(cfg, tensors, tokens, dtype=torch.float64, layers_out=None, choices=None, margins=None):
     """Logits [T, vocab] of one sequence.  ``layers_out``: a list that receives the sum of the streams after every layer run.
-    ``choices``: {(run, token): experts} to take instead of the router's; ``margins``: a list that receives every routed
-    layer's margins."""
+    ``choices``: per routed feed-forward that runs, in order, the experts [T, top] to take instead of the router's own;
+    ``margins``: a list that receives (the router's own experts, its margins) of every routed feed-forward that runs."""
     t = {k: torch.as_tensor(v).to(dtype) for k, v in tensors.items()}
     eps, S = cfg["norm"]["eps"], cfg.get("streams", 1)
     x = t["embed"][torch.tensor(tokens)]
     xs = x[None].repeat(S, 1, 1)
-    for run, i in enumerate(layer_order(cfg)):
+    routed = 0
+    for i in layer_order(cfg):
         layer, p = cfg["layers"][i], f"l{i}."
-        subs = [(1, lambda h: mixer(layer["type"], h, _sub(t, p + "mix."), layer["mixer"], eps))]
-        if layer.get("mlp") is not None:
-            def ff(h, run=run):
-                y, idx, margin = routed_ff(h, _sub(t, p + "mlp."), layer["mlp"], None if choices is None else choices.get(run))
+        for q in (1, 2):
+            if q == 2 and layer.get("mlp") is None:
+                continue
+            h = rms_norm(hyper_read(xs, t[f"{p}hc{q}.in"]), t[f"{p}norm{q}"], eps)
+            if q == 1:
+                y = mixer(layer["type"], h, _sub(t, p + "mix."), layer["mixer"], eps)
+            else:
+                y, idx, margin = routed_ff(h, _sub(t, p + "mlp."), layer["mlp"], None if choices is None else choices[routed])
+                routed += 1
                 if margins is not None:
-                    margins.append((run, idx, margin))
-                return y
-            subs.append((2, ff))
-        for q, fn in subs:
-            u = hyper_read(xs, t[f"{p}hc{q}.in"])
-            y = fn(rms_norm(u, t[f"{p}norm{q}"], eps))
+                    margins.append((idx, margin))
             xs = hyper_write(xs, y, t[f"{p}hc{q}.mix"], t[f"{p}hc{q}.out"])
         if layers_out is not None:
             layers_out.append(xs.sum(dim=0))
