@@ -162,7 +162,7 @@ def main():
     ap.add_argument("--no-points", action="store_true", help="skip batch 1 / 64 and the prefill")
     ap.add_argument("--no-shapes", action="store_true", help="skip the Llama-3-8B and Qwen2.5-7B shaped points")
     ap.add_argument("--block-size", type=int, default=64, help="tokens per cache page (named in config)")
-    ap.add_argument("--design", default=None, choices=["zatupel", "tidenex", "tuzavik"],
+    ap.add_argument("--design", default=None, choices=["zatupel", "tidenex", "tuzavik", "natalorn"],
                     help="instead of the default workload: prefill and decode speed of that design at a few layer sizes, "
                          "beside the LLaMA decoder of equal width, depth and head counts")
     a = ap.parse_args()
@@ -608,8 +608,94 @@ class TuzavikBench(ShapeBench):
         return flops
 
 
+def natalorn_shape(width, layers, heads, kv_heads, dim, ff, window, vocab, **_):
+    """A Natalorn configuration at a real model's layer sizes: a stream of four copies; layers in turn windowed attention, latent
+    attention (``heads`` heads of ``dim`` unrotated, dim/2 rotated and ``dim`` value channels over a latent of 4*dim channels, queries
+    through a latent of 3/4 of the width, a window, sinks, a gate), windowed attention, chunked attention with capped scores and
+    biases; every layer with 8 experts of a quarter of the dense width in 4 groups of which 2 are kept, 2 a token, beside a shared
+    expert of half the dense width, so that a token passes through as many feed-forward weights as in the other decoders."""
+    att = {"type": "attention", "mixer": {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": dim, "mask": {"size": window}, "scale": dim ** -0.5}}
+    att2 = {"type": "attention_2", "mixer": {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": dim, "mask": {"size": window},
+                                             "scale": dim ** -0.5, "softcap": 50.0}}
+    lat = {"type": "latent_attention", "mixer": {"heads": heads, "dim": dim, "rot_dim": dim // 2, "vdim": dim, "kv_rank": 4 * dim,
+                                                 "q_rank": 3 * width // 4, "mask": {"size": window}, "scale": (dim + dim // 2) ** -0.5,
+                                                 "rot": {"dims": dim // 2, "base": 10000.0}}}
+    moe = {"kind": "moe", "expert": {"ff": ff // 4}, "router": {"experts": 8, "top": 2, "scale": 1.5, "groups": {"count": 4, "keep": 2}},
+           "shared": {"ff": ff // 2}}
+    order = (att, lat, att, att2)
+    return {"architecture": "Natalorn", "vocab": vocab, "width": width, "norm": {"eps": 1e-5}, "streams": 4, "max_positions": 8192,
+            "layers": [dict(order[i % 4], mlp=moe) for i in range(layers)]}
+
+
+def natalorn_matmul_params(cfg, experts_read=None):
+    """Matrix elements of all layer runs that a token passes through (``experts_read`` None: its ``top`` experts) or that a step reads
+    (``experts_read``: how many experts of a routed layer), and of the head."""
+    W, total = cfg.width, 0
+    for i in cfg.schedule():
+        layer = cfg.layers[i]
+        m = layer["mixer"]
+        if layer["type"] == "latent_attention":
+            H, D, R, E, C, Cq = m["heads"], m["dim"], m["rot_dim"], m["vdim"], m["kv_rank"], m["q_rank"]
+            total += W * Cq + Cq * H * (D + R) + W * (C + R) + H * D * C + H * E * C + 2 * W * H * E
+        else:
+            H, G, D, E = m["heads"], m.get("kv_heads", m["heads"]), m["dim"], m.get("vdim", m["dim"])
+            total += W * (H * D + G * D + G * E) + W * H * E
+        mlp = layer.get("mlp")
+        if mlp:
+            n = mlp["router"]["top"] if experts_read is None else min(mlp["router"]["experts"], experts_read)
+            total += 3 * W * mlp["expert"]["ff"] * n + W * mlp["router"]["experts"] + 3 * W * (mlp.get("shared") or {}).get("ff", 0)
+    return total, cfg.vocab * W
+
+
+def _visible_pairs(T, window=None, chunk=None):
+    """How many (token, key) pairs T tokens of one sequence see."""
+    if chunk:
+        full, rest = divmod(T, chunk)
+        return full * chunk * (chunk + 1) // 2 + rest * (rest + 1) // 2
+    w = min(window or T, T)
+    return w * (w + 1) // 2 + (T - w) * w
+
+
+class NatalornBench(ShapeBench):
+    """ShapeBench's measurements for a Natalorn configuration: only bytes and FLOPs are counted otherwise."""
+
+    def decode_bytes(self, B, ctx):
+        """Every matrix that the step reads once (of a routed layer the experts that B tokens can choose, and the shared one), per
+        request the keys and values (or latent rows) inside every layer's window or chunk, and the stream's copies read and written
+        by every sublayer."""
+        cfg = self.cfg
+        top = max([l["mlp"]["router"]["top"] for l in cfg.layers if l.get("mlp")] or [1])
+        layers, head = natalorn_matmul_params(cfg, experts_read=B * top)
+        total = 2 * (layers + head)
+        for i in cfg.schedule():
+            layer = cfg.layers[i]
+            m = layer["mixer"]
+            size = m["mask"]["size"]
+            seen = (ctx % size) + 1 if layer["type"] == "attention_2" else min(ctx, size)
+            if layer["type"] == "latent_attention":
+                total += B * seen * (m["kv_rank"] + m["rot_dim"]) * 2
+            else:
+                total += B * seen * m.get("kv_heads", m["heads"]) * (m["dim"] + m.get("vdim", m["dim"])) * 2
+            total += B * (2 if layer.get("mlp") else 1) * 2 * cfg.streams * cfg.width * 4
+        return total
+
+    def prefill_flops(self, T):
+        """Products, and the attention as the design states it (per visible pair and head: scores over dim (+ rot_dim) channels, values
+        of vdim; the latent attention's absorbed form executes kv_rank + rot_dim and kv_rank instead)."""
+        cfg = self.cfg
+        layers, head = natalorn_matmul_params(cfg)
+        flops = 2 * T * layers + 2 * head
+        for i in cfg.schedule():
+            layer = cfg.layers[i]
+            m = layer["mixer"]
+            size = m["mask"]["size"]
+            pairs = _visible_pairs(T, chunk=size) if layer["type"] == "attention_2" else _visible_pairs(T, window=size)
+            flops += 2 * pairs * m["heads"] * (m["dim"] + m.get("rot_dim", 0) + m.get("vdim", m["dim"]))
+        return flops
+
+
 def design_arm(a):
-    """Prefill and decode speed of the Zatupel, Tidenex or Tuzavik design at a few layer sizes (random weights), each beside the LLaMA decoder
+    """Prefill and decode speed of the Zatupel, Tidenex, Tuzavik or Natalorn design at a few layer sizes (random weights), each beside the LLaMA decoder
     of the same width, depth, head counts and feed-forward width run the same way: decode device-timed at batch 1, 8 and
     64 after 512-token prompts, one prompt step of 2,048 tokens.  One JSON line."""
     import torch
@@ -639,6 +725,8 @@ def design_arm(a):
             arms.insert(0, ("tidenex", tidenex_shape(**z), TidenexBench))
         if a.design == "tuzavik":         # beside the design whose state scan and attention kernels are the nearest, and the plain decoder
             arms = [("tuzavik", tuzavik_shape(**z), TuzavikBench), ("tidenex", tidenex_shape(**z), TidenexBench), arms[1]]
+        if a.design == "natalorn":        # beside the design whose latent attention and routed experts are its own, and the plain decoder
+            arms = [("natalorn", natalorn_shape(**z), NatalornBench), ("tuzavik", tuzavik_shape(**z), TuzavikBench), arms[1]]
         for arch, shape, maker in arms:
             b = maker(shape, PROMPT_LEN, 64, steps, a.warmup, a.block_size, prefill_tokens=PREFILL_TOKENS)
             r = {}

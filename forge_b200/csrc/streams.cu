@@ -29,13 +29,21 @@ streams_expand_kernel(const float* __restrict__ e, float* __restrict__ x, int S,
 }
 
 // One CTA per row.  rows (or null) picks the tokens; with y the copies of the token are rewritten.  u (dynamic shared
-// memory, W floats) holds what the norm reads between the two walks.
-template <typename TOut, int S>
+// memory, W floats) holds what the norm reads between the two walks.  V = 4: rows of a multiple of four channels on 16-byte
+// boundaries go four channels a load (every channel's arithmetic is what V = 1 does).
+template <int V> struct Pack;
+template <> struct Pack<1> { using type = float; };
+template <> struct Pack<4> { using type = float4; };
+__device__ __forceinline__ float& lane_of(float& v, int) { return v; }
+__device__ __forceinline__ float& lane_of(float4& v, int i) { return (&v.x)[i]; }
+
+template <typename TOut, int S, int V>
 __global__ void __launch_bounds__(kThreads)
 streams_mix_kernel(float* __restrict__ x, const float* __restrict__ y, const float* __restrict__ mix, const float* __restrict__ outc,
                    const float* __restrict__ in_next, const float* __restrict__ w_next, TOut* __restrict__ normed,
                    const int32_t* __restrict__ rows, int W, float eps) {
-    extern __shared__ float u[];
+    using P = typename Pack<V>::type;
+    extern __shared__ __align__(16) float u[];
     __shared__ float red[32];
     __shared__ float cm[S * S], cb[S], ca[S];
     forge::pdl_launch_dependents();
@@ -50,30 +58,36 @@ streams_mix_kernel(float* __restrict__ x, const float* __restrict__ y, const flo
     float* xr = x + (size_t)t * S * W;
     const float* yr = y ? y + (size_t)t * W : nullptr;
     float ss = 0.f;
-    for (int c = threadIdx.x; c < W; c += kThreads) {
-        float old[S], cur[S];
+    for (int c = threadIdx.x * V; c < W; c += kThreads * V) {
+        P old[S], cur[S];
 #pragma unroll
-        for (int s = 0; s < S; ++s) old[s] = xr[(size_t)s * W + c];
+        for (int s = 0; s < S; ++s) old[s] = *reinterpret_cast<const P*>(xr + (size_t)s * W + c);
         if (yr) {
-            const float yv = yr[c];
+            P yv = *reinterpret_cast<const P*>(yr + c);
 #pragma unroll
             for (int k = 0; k < S; ++k) {
-                float a = 0.f;
 #pragma unroll
-                for (int s = 0; s < S; ++s) a = fmaf(cm[s * S + k], old[s], a);
-                cur[k] = fmaf(cb[k], yv, a);
-                xr[(size_t)k * W + c] = cur[k];
+                for (int i = 0; i < V; ++i) {
+                    float a = 0.f;
+#pragma unroll
+                    for (int s = 0; s < S; ++s) a = fmaf(cm[s * S + k], lane_of(old[s], i), a);
+                    lane_of(cur[k], i) = fmaf(cb[k], lane_of(yv, i), a);
+                }
+                *reinterpret_cast<P*>(xr + (size_t)k * W + c) = cur[k];
             }
         } else {
 #pragma unroll
             for (int s = 0; s < S; ++s) cur[s] = old[s];
         }
         if (in_next) {
-            float a = 0.f;
 #pragma unroll
-            for (int s = 0; s < S; ++s) a = fmaf(ca[s], cur[s], a);
-            u[c] = a;
-            ss = fmaf(a, a, ss);
+            for (int i = 0; i < V; ++i) {
+                float a = 0.f;
+#pragma unroll
+                for (int s = 0; s < S; ++s) a = fmaf(ca[s], lane_of(cur[s], i), a);
+                u[c + i] = a;
+                ss = fmaf(a, a, ss);
+            }
         }
     }
     if (!in_next) return;
@@ -83,21 +97,32 @@ streams_mix_kernel(float* __restrict__ x, const float* __restrict__ y, const flo
     for (int c = threadIdx.x; c < W; c += kThreads) o[c] = forge::from_float<TOut>(u[c] * inv * w_next[c]);
 }
 
-template <typename TOut, int S>
-cudaError_t launch_mix(cudaStream_t stream, int R, float* x, const float* y, const float* mix, const float* outc, const float* in_next,
-                       const float* w_next, void* normed, const int32_t* rows, int W, float eps) {
+template <typename TOut, int S, int V>
+cudaError_t launch_mix_v(cudaStream_t stream, int R, float* x, const float* y, const float* mix, const float* outc, const float* in_next,
+                         const float* w_next, void* normed, const int32_t* rows, int W, float eps) {
     const size_t smem = in_next ? sizeof(float) * W : 0;
     if (smem > 48 * 1024) {
         static forge::PerDeviceFlag attr;
         bool& done = attr.current();
         if (!done) {
-            cudaError_t e = cudaFuncSetAttribute(streams_mix_kernel<TOut, S>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+            cudaError_t e = cudaFuncSetAttribute(streams_mix_kernel<TOut, S, V>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
             if (e != cudaSuccess) return e;
             done = true;
         }
     }
-    return forge::launch(streams_mix_kernel<TOut, S>, dim3(R), dim3(kThreads), smem, stream, 1, x, y, mix, outc, in_next, w_next,
+    return forge::launch(streams_mix_kernel<TOut, S, V>, dim3(R), dim3(kThreads), smem, stream, 1, x, y, mix, outc, in_next, w_next,
                          (TOut*)normed, rows, W, eps);
+}
+
+template <typename TOut, int S>
+cudaError_t launch_mix(cudaStream_t stream, int R, float* x, const float* y, const float* mix, const float* outc, const float* in_next,
+                       const float* w_next, void* normed, const int32_t* rows, int W, float eps) {
+    // four channels a load keep 8 S numbers in registers: up to four copies
+    if constexpr (S <= 4) {
+        if ((W & 3) == 0 && (((uintptr_t)x | (uintptr_t)y) & 15) == 0)
+            return launch_mix_v<TOut, S, 4>(stream, R, x, y, mix, outc, in_next, w_next, normed, rows, W, eps);
+    }
+    return launch_mix_v<TOut, S, 1>(stream, R, x, y, mix, outc, in_next, w_next, normed, rows, W, eps);
 }
 
 }  // namespace

@@ -215,6 +215,49 @@ def case(name):
         pairs = sum(c + j + 1 for c, n in reqs for j in range(n))
         return (lambda: latent_attention(q, cache, g, batch, Hh, C, R, ps, (C + R) ** -0.5)), \
             pairs * (C + R) * 2 // max(1, T // len(reqs)), 2 * pairs * Hh * (2 * C + R)
+    if name in ("windowed_attention_prefill", "chunked_attention_prefill", "windowed_attention_decode", "windowed_latent_prefill", "windowed_latent_decode"):
+        # attention without rotation over a window of 1,024 positions (32 / 4 kv heads of 64), the same in chunks of 1,024 with scores
+        # capped at 50, and attention over latent rows (32 heads, 256 + 32 channels) in a window of 1,024 with a sink per head: one
+        # prompt of 4,096 tokens, or 8 requests of 2,047 cached tokens and one new one.  FLOPs as executed, visible pairs only
+        from forge_b200.kernels import latent_attention, scored_attention
+        ps, size = 64, 1024
+        latent, chunked = "latent" in name, name.startswith("chunked")
+        Hh, G, D, E, C, R = 32, 4, 64, 64, 256, 32
+        reqs = [(2047, 1)] * 8 if name.endswith("decode") else [(0, 4096)]
+        pages_per = [-(-(c + n) // ps) for c, n in reqs]
+        table = torch.full((len(reqs), max(pages_per)), -1, dtype=torch.int32)
+        q_start, nxt = [0], 0
+        for s_, n in enumerate(pages_per):
+            table[s_, :n] = torch.arange(nxt, nxt + n, dtype=torch.int32)
+            nxt += n
+            q_start.append(q_start[-1] + reqs[s_][1])
+        T = q_start[-1]
+        i32 = lambda x: torch.tensor(x, dtype=torch.int32, device=DEV)
+        batch = SimpleNamespace(num_requests=len(reqs), num_tokens=T, host_q_start=q_start, attention_plan={},
+                                tok_req=i32([s_ for s_, (c, n) in enumerate(reqs) for _ in range(n)]),
+                                positions=i32([c + j for c, n in reqs for j in range(n)]))
+        if name.endswith("decode"):
+            batch.decode_only, batch.max_context = True, 2048
+        g = SimpleNamespace(block_table=table.to(DEV))
+        seen = lambda p: (p % size) + 1 if chunked else min(p + 1, size)
+        pairs = sum(seen(c + j) for c, n in reqs for j in range(n))
+        if latent:
+            q, cache, sink = _bf16(T, Hh * (C + R), scale=0.3), _bf16(nxt, ps * (C + R)), torch.randn(Hh, device=DEV)
+            return (lambda: latent_attention(q, cache, g, batch, Hh, C, R, ps, (C + R) ** -0.5, window=size, sink=sink)), \
+                pairs * (C + R) * 2 // max(1, T // len(reqs)), 2 * pairs * Hh * (2 * C + R)
+        q, cache = _bf16(T, Hh * D), _bf16(nxt, G * ps * (D + E))
+        return (lambda: scored_attention(q, cache, g, batch, Hh, G, 1, D, E, ps, D ** -0.5, window=0 if chunked else size,
+                                         chunk=size if chunked else 0, softcap=50.0 if chunked else 0.0)), \
+            pairs * G * (D + E) * 2 // max(1, T // len(reqs)), 2 * pairs * Hh * (D + E)
+    if name in ("streams_mix_prefill", "streams_mix_decode"):
+        # a stream of four copies of 2,048 channels: a sublayer's write and the next sublayer's read and norm in one pass, for 4,096
+        # tokens (the copies read and written once: 268 MB) or 8
+        from forge_b200.kernels import streams_mix
+        T, S, W_ = (4096 if name.endswith("prefill") else 8), 4, 2048
+        xs, y = torch.randn(T, S * W_, device=DEV), torch.randn(T, W_, device=DEV)
+        mix, ow, iw, wn = torch.eye(S, device=DEV), torch.ones(S, device=DEV) * 0.1, torch.ones(S, device=DEV) * 0.25, torch.ones(W_, device=DEV)
+        return (lambda: streams_mix(xs, S, y=y, mix=mix, out_w=ow, in_next=iw, w_next=wn, eps=1e-5, out_dtype=torch.bfloat16)), \
+            T * W_ * (2 * S * 4 + 4 + 2), 2 * T * W_ * S * (S + 2)
     if name == "routed_pairs_decode":
         # routed experts, one token: 2 of 8 experts of [7168 x 4096] gate, up and down matrices, each (token, expert) pair streaming
         # its expert's rows once (352 MB read, far more than L2 holds); router included
@@ -247,7 +290,7 @@ def case(name):
             kk.copy_(k0)
             retention_scan((qq, 0), (kk, 0), (v, 0), batch, freq, K ** -0.5, decay, state, N, K, K)
         return run, 3 * T * N * K * 4, 4 * T * N * K * K
-    raise SystemExit(f"unknown case {name!r}; known: routed_pairs_decode latent_attention_prefill latent_attention_prefill_512 latent_attention_decode retention_scan scored_attention_prefill scored_attention_decode distance_attention_prefill state_scan_gated headmix_attention_prefill headmix_attention_decode state_scan_wkv state_scan_delta "
+    raise SystemExit(f"unknown case {name!r}; known: windowed_attention_prefill chunked_attention_prefill windowed_attention_decode windowed_latent_prefill windowed_latent_decode streams_mix_prefill streams_mix_decode routed_pairs_decode latent_attention_prefill latent_attention_prefill_512 latent_attention_decode retention_scan scored_attention_prefill scored_attention_decode distance_attention_prefill state_scan_gated headmix_attention_prefill headmix_attention_decode state_scan_wkv state_scan_delta "
                      "gemm_decode_gateup gemm_decode_down gemm_decode_lmhead gemm_prefill_qkv "
                      "gemm_prefill_gateup "
                      "gemm_prefill_qkv_rope gemm_prefill_down attention_decode attention_decode_fused attention_decode_stream attention_prefill "

@@ -88,3 +88,25 @@ def test_the_third_design_option_too():
     assert layers == matrices and head == 300 * 256
     per_token, _ = bench.tuzavik_matmul_params(cfg)
     assert layers - per_token == 2 * 6 * 3 * 256 * 256                    # six of eight experts of two routed layers
+
+
+def test_the_fourth_design_option_too():
+    rc, lines = _run("--design", "natalorn", "--gpus", "2")
+    assert rc == 2 and len(lines) == 1 and "single-GPU" in json.loads(lines[0])["error"]
+    sys.path.insert(0, ROOT)
+    import bench
+    import torch
+    from forge_b200.config import config_from_dict
+    from forge_b200.engine.model import Model
+    from forge_b200.parts import Runtime
+    z = dict(width=256, layers=5, heads=8, kv_heads=2, dim=32, ff=512, state_heads=4, state_dim=32, rank=16, window=64, vocab=300)
+    cfg = config_from_dict(bench.natalorn_shape(**z))
+    assert [l["type"] for l in cfg.layers] == ["attention", "latent_attention", "attention", "attention_2", "attention"] and cfg.streams == 4
+    # counted from the configuration alone with every expert read, the matrices are what the model's own tensor list holds
+    layers, head = bench.natalorn_matmul_params(cfg, experts_read=8)
+    specs = Model(cfg.plan(), Runtime(torch.device("cpu"), torch.bfloat16)).tensor_specs()
+    matrices = sum(s.shape[0] * s.shape[1] for n, s in specs.items() if len(s.shape) == 2 and s.required and n not in ("embed", "head") and ".hc" not in n)
+    assert layers == matrices and head == 300 * 256
+    per_token, _ = bench.natalorn_matmul_params(cfg)
+    assert layers - per_token == 5 * 6 * 3 * 256 * 128                    # six of eight experts of five routed layers
+    assert bench._visible_pairs(10, window=4) == 1 + 2 + 3 + 7 * 4 and bench._visible_pairs(10, chunk=4) == 10 + 10 + 3
