@@ -51,6 +51,13 @@ __device__ __forceinline__ float ex2(float x) {          // 2^x, relative error 
     asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
     return y;
 }
+// tanh(x) = 1 - 2 / (e^(2x) + 1) from the approximate exponential and reciprocal: absolute error about 2e-7 (and exactly +-1
+// far out), which a score from bfloat16 operands does not see; the kernel of fp32 arithmetic keeps tanhf
+__device__ __forceinline__ float tanh_fast(float x) {
+    float r;
+    asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(ex2(x * 2.8853900817779268f) + 1.0f));
+    return fmaf(-2.0f, r, 1.0f);
+}
 __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
     __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
     return *reinterpret_cast<uint32_t*>(&v);
@@ -201,7 +208,7 @@ scored_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __re
                         const bool ok = (hi ? live_hi : live_lo) && j <= pos && j >= (hi ? see_hi : see_lo);
                         float s = -INFINITY;
                         if (ok) {
-                            s = softcap > 0.f ? cap_out * tanhf(sacc[nt][e] * cap_in) : sacc[nt][e] * sl2;
+                            s = softcap > 0.f ? cap_out * tanh_fast(sacc[nt][e] * cap_in) : sacc[nt][e] * sl2;
                             // r1 ln(1 + r2 d) in units of log2(e) is r1 log2(1 + r2 d); lg2.approx errs by 2^-22, far below
                             // the rounding of the bfloat16 operands of q . k
                             if (r1) s -= r1v[hi] * __log2f(fmaf(r2v[hi], (float)(pos - j), 1.0f));

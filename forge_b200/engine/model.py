@@ -205,6 +205,9 @@ class Model:
                 if replay is not None:
                     replay.run(self._replay_tensors[pos] + [position_caches[pos].kv])
                     continue
+                if S != 1:
+                    # a block may leave the next block's first input in the same pass as its own last write to the copies
+                    batch.shared["following_block"] = self.blocks[self.plan.schedule[pos + 1]] if pos + 1 < len(self.plan.schedule) else None
                 # one layer's launches are noted and repeated for the layers after it (what the whole step shares,
                 # tile lists and the table of angles, is made inside the first layer: those launches are marked
                 # and stay out of the notes)

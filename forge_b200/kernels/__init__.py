@@ -590,11 +590,12 @@ def streams_expand(x, S):
     return out
 
 
-def streams_mix(xs, S, y=None, mix=None, out_w=None, in_next=None, w_next=None, eps=0.0, out_dtype=None, rows=None):
+def streams_mix(xs, S, y=None, mix=None, out_w=None, in_next=None, w_next=None, eps=0.0, out_dtype=None, rows=None, out=None):
     """xs fp32 [T, S*W], the S copies of the stream.  With ``y`` fp32 [T, W] (a sublayer's output) every copy is rewritten at once
     from the old ones, copy t <- sum_s mix[s, t] copy_s + out_w[t] y (mix fp32 [S, S], out_w fp32 [S]).  With ``in_next`` fp32 [S]
     and ``w_next`` fp32 [W] returns rmsnorm(sum_s in_next[s] copy_s) * w_next of the (new) copies in ``out_dtype``, else None.
-    ``rows`` int32 [R] (reading only): the tokens whose rows are wanted."""
+    ``rows`` int32 [R] (reading only): the tokens whose rows are wanted.  ``out``: the tensor that receives the normed rows instead
+    of a new one."""
     lib = library("core")
     T, SW = xs.shape
     W = SW // S
@@ -604,7 +605,12 @@ def streams_mix(xs, S, y=None, mix=None, out_w=None, in_next=None, w_next=None, 
             or (w_next is not None and w_next.numel() != W):
         raise KernelError("streams_mix: weights of the wrong size")
     R = T if rows is None else rows.numel()
-    out = new_tensor((R, W), out_dtype, xs.device) if in_next is not None else None
+    if in_next is None:
+        out = None
+    elif out is None:
+        out = new_tensor((R, W), out_dtype, xs.device)
+    elif tuple(out.shape) != (R, W) or out.dtype != out_dtype:
+        raise KernelError(f"streams_mix: the output given is {tuple(out.shape)} {out.dtype}, the normed rows are {(R, W)} {out_dtype}")
     _check(lib, lib.forge_streams_mix(
         _need(xs, "xs", torch.float32, 2), _opt(y, "y", torch.float32), _opt(mix, "mix", torch.float32), _opt(out_w, "out_w", torch.float32),
         _opt(in_next, "in_next", torch.float32), _opt(w_next, "w_next", torch.float32), _opt(out, "out", out_dtype),

@@ -10,7 +10,8 @@ sublayer's input norm are one kernel.
 "hyper_connections":  the stream is S copies x_1 .. x_S (all equal to the embedding output at the start; their sum is what the
 model's last norm reads).  Around sublayer q (1: mixer, 2: feed-forward), with weights in_q [S], out_q [S], mix_q [S, S]:
     u = sum_s in_q[s] x_s;   y = sublayer(norm_q(u));   x_t <- sum_s mix_q[s, t] x_s + out_q[t] y   (all t at once, from the old copies)
-in place of the residual sum.  A sublayer's write and the next sublayer's read and norm are one kernel.
+in place of the residual sum.  A sublayer's write and the next sublayer's read and norm are one kernel, also across layers: where the
+model says which block runs next (``batch.shared["following_block"]``), a layer's last write leaves that block's first input.
 """
 from ..weights.loader import TensorSpec  # noqa: F401  (re-exported for part authors)
 from .base import Part, build_part, register_part
@@ -234,18 +235,40 @@ class HyperConnectionBlock(Part):
             for k in ("in", "out", "mix"):
                 self.weights[f"{q}.{k}"] = self._vector_f32(tensors[f"hc{q}.{k}"])
 
+    def _last_write(self, residual, batch, y, q):
+        """The layer's last write; where the block that runs next is one of this kind, the same pass leaves its first input (in one
+        of two buffers that live as long as the step, taken in turn) under ``batch.shared["stream_input"]``."""
+        from .. import kernels
+        S, w = self.streams, self.weights
+        nxt = batch.shared.get("following_block")
+        if not isinstance(nxt, HyperConnectionBlock) or nxt.streams != S or nxt.rt.dtype != self.rt.dtype:
+            kernels.streams_mix(residual, S, y=y, mix=w[f"{q}.mix"], out_w=w[f"{q}.out"])
+            return
+        bufs = batch.shared.setdefault("stream_input_buffers", [None, None])
+        turn = batch.shared["stream_input_turn"] = 1 - batch.shared.get("stream_input_turn", 1)
+        if bufs[turn] is None:
+            bufs[turn] = kernels.new_tensor((y.shape[0], y.shape[1]), self.rt.dtype, y.device, whole_step=True)
+        n1 = nxt.norms["mixer_in"]
+        x = kernels.streams_mix(residual, S, y=y, mix=w[f"{q}.mix"], out_w=w[f"{q}.out"], in_next=nxt.weights["1.in"], w_next=n1.weight,
+                                eps=n1.eps, out_dtype=self.rt.dtype, out=bufs[turn])
+        batch.shared["stream_input"] = (nxt, x)
+
     def forward(self, residual, batch, cache):
         from .. import kernels
         S, w, n1, n2 = self.streams, self.weights, self.norms["mixer_in"], self.norms["ff_in"]
-        x = kernels.streams_mix(residual, S, in_next=w["1.in"], w_next=n1.weight, eps=n1.eps, out_dtype=self.rt.dtype)
+        left = batch.shared.pop("stream_input", None)          # (the block it is meant for, its first input) from the layer before
+        if left is not None and left[0] is self:
+            x = left[1]
+        else:
+            x = kernels.streams_mix(residual, S, in_next=w["1.in"], w_next=n1.weight, eps=n1.eps, out_dtype=self.rt.dtype)
         y = self.mixer.forward(x, batch, cache, None)
         if n2 is None:
-            kernels.streams_mix(residual, S, y=y, mix=w["1.mix"], out_w=w["1.out"])
+            self._last_write(residual, batch, y, 1)
             return
         x = kernels.streams_mix(residual, S, y=y, mix=w["1.mix"], out_w=w["1.out"], in_next=w["2.in"], w_next=n2.weight, eps=n2.eps,
                                 out_dtype=self.rt.dtype)
         y = self.feed_forward.forward(x, None)
-        kernels.streams_mix(residual, S, y=y, mix=w["2.mix"], out_w=w["2.out"])
+        self._last_write(residual, batch, y, 2)
 
 
 def build_block(layer_spec, rt):
