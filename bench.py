@@ -676,7 +676,7 @@ class NatalornBench(ShapeBench):
                 total += B * seen * (m["kv_rank"] + m["rot_dim"]) * 2
             else:
                 total += B * seen * m.get("kv_heads", m["heads"]) * (m["dim"] + m.get("vdim", m["dim"])) * 2
-            total += B * (2 if layer.get("mlp") else 1) * 2 * cfg.streams * cfg.width * 4
+            total += B * (2 if layer.get("mlp") else 1) * 2 * (cfg.streams or 1) * cfg.width * 4
         return total
 
     def prefill_flops(self, T):

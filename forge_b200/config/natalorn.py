@@ -1,7 +1,8 @@
 """Typed configuration of the Natalorn decoder: pre-norm layers (RMS norms) listed in config.json on a residual stream that is
 kept as ``streams`` copies (hyper-connections: every sublayer reads a weighted sum of the copies and its output rewrites all of
 them through a small mixing matrix), each layer with one of three mixers and a routed feed-forward or none; a span of the layers
-may run several times in a row with the same weights, every pass with a cache of its own; untied output head.
+may run several times in a row with the same weights, every pass with a cache of its own; untied output head.  A config.json without
+``streams`` describes the same decoder on one ordinary residual stream (x <- x + sublayer(norm(x)), no ``hc`` tensors).
 
   "attention"         grouped-query softmax attention without rotation over a sliding window (``mask.size`` positions)
   "attention_2"       the same with q/k/v biases, scores capped by ``softcap`` tanh(score / ``softcap``), and chunks instead of a
@@ -47,7 +48,7 @@ class NatalornConfig:
     vocab: int
     width: int
     norm_eps: float
-    streams: int = 1
+    streams: Optional[int] = None          # None: one ordinary residual stream, no hyper-connection weights
     layers: List[Dict[str, Any]] = field(default_factory=list)
     loop: Optional[Dict[str, int]] = None
     max_positions: int = DEFAULT_MAX_POSITIONS
@@ -75,7 +76,7 @@ class NatalornConfig:
         if loop is not None:
             loop = {k: require(_section(d, "loop", ""), k, int) for k in ("start", "stop", "times")}
         cfg = cls(architecture=architecture, vocab=require(d, "vocab", int), width=require(d, "width", int),
-                  norm_eps=require(_section(d, "norm", ""), "eps", float), streams=optional(d, "streams", int, 1),
+                  norm_eps=require(_section(d, "norm", ""), "eps", float), streams=optional(d, "streams", int, None),
                   layers=copy.deepcopy(layers), loop=loop, max_positions=optional(d, "max_positions", int, DEFAULT_MAX_POSITIONS),
                   eos_token_id=optional(d, "eos_token_id", int, None))
         cfg.validate()
@@ -84,7 +85,7 @@ class NatalornConfig:
     def validate(self):
         if self.vocab <= 0 or self.width <= 0 or self.max_positions <= 0 or not self.norm_eps > 0.0:
             raise ConfigError("config.json: vocab, width, max_positions and norm.eps must be positive")
-        if not 1 <= self.streams <= 16:
+        if self.streams is not None and not 1 <= self.streams <= 16:
             raise ConfigError("config.json: 'streams' must lie between 1 and 16")
         for i, layer in enumerate(self.layers):
             where = f"layers[{i}]: "
@@ -132,7 +133,9 @@ class NatalornConfig:
 
     def to_dict(self):
         d = {"architecture": self.architecture, "layers": copy.deepcopy(self.layers), "norm": {"eps": self.norm_eps},
-             "streams": self.streams, "vocab": self.vocab, "width": self.width}
+             "vocab": self.vocab, "width": self.width}
+        if self.streams is not None:
+            d["streams"] = self.streams
         if self.loop is not None:
             d["loop"] = dict(self.loop)
         if self.max_positions != DEFAULT_MAX_POSITIONS:
@@ -188,6 +191,11 @@ class NatalornConfig:
         layers = []
         for i, layer in enumerate(self.layers):
             mlp = layer.get("mlp")
+            if self.streams is None:
+                layers.append(LayerSpec(block="pre_norm", mixer=self._mixer(layer), feed_forward=self._feed_forward(mlp),
+                                        norms={"input": norm("norm1"), "post_mixer": None if mlp is None else norm("norm2")},
+                                        weight_prefix=f"l{i}.", norm_prefixes={"input": "", "post_mixer": ""}))
+                continue
             layers.append(LayerSpec(block="hyper_connections", mixer=self._mixer(layer), feed_forward=self._feed_forward(mlp),
                                     norms={"mixer_in": norm("norm1"), "ff_in": None if mlp is None else norm("norm2")},
                                     weight_prefix=f"l{i}.", block_params={"streams": self.streams}))
@@ -196,4 +204,4 @@ class NatalornConfig:
             embedding=PartSpec("embedding", {"vocab_size": self.vocab, "hidden_size": W, "names": {"weight": "embed"}}),
             final_norm=norm("final.norm"),
             lm_head=PartSpec("lm_head", {"vocab_size": self.vocab, "hidden_size": W, "tied": False, "names": {"weight": "head"}}),
-            layers=layers, schedule=self.schedule(), embedding_prefix="", final_norm_prefix="", lm_head_prefix="", streams=self.streams)
+            layers=layers, schedule=self.schedule(), embedding_prefix="", final_norm_prefix="", lm_head_prefix="", streams=self.streams or 1)

@@ -1,13 +1,14 @@
 """Small Natalorn configurations for the tests, and model folders with random weights made from them.
 
-The three differ in every size, in the order and number of the layers, in the repeated span and in every constant; among them
+The first three differ in every size, in the order and number of the layers, in the repeated span and in every constant; among them
 they have what a single model can hide: one copy of the stream, two and four; no repeated span, one in the middle and one over
 all layers; attention with as many key/value heads as query heads, with one, and with a number between; value heads narrower
 and wider than key heads; windows shorter than a page, of one position, and longer than any sequence; chunks shorter than a
 page, of a page and a half, and longer than any sequence; a cap on the scores that bites and one that does not; a latent
 narrower and wider than a head, rotated parts of other widths than the unrotated ones; a layer without a feed-forward; experts
 in one group, in groups that are all kept, and in groups of which some are dropped; one expert a token and all experts of the
-kept groups; a router factor above and below one; a layer without a shared expert.
+kept groups; a router factor above and below one; a layer without a shared expert; and (N) the same decoder on one ordinary
+residual stream, without the weights of the copies.
 """
 import copy
 
@@ -61,11 +62,16 @@ NAT = {
           "layers": [_moe(_lat(4, 32, 16, 48, 96, 64, 70, 0.15, 250000.0), 128, 8, 2, 1.5, groups=(4, 2), shared=64),
                      _moe(_att(8, 2, 32, 24, 100, 0.2), 64, 4, 2, 0.9, groups=(2, 2), shared=128),
                      _moe(_att2(4, 4, 64, 64, 72, 0.12, 4.0), 128, 6, 3, 1.2, groups=(2, 1), shared=64)]},
+    # no 'streams': x <- x + sublayer(norm(x))
+    "N": {"architecture": "Natalorn", "vocab": 97, "width": 64, "norm": {"eps": 1e-5}, "loop": {"start": 0, "stop": 1, "times": 2},
+          "layers": [_moe(_att2(4, 2, 16, 8, 24, 0.3, 5.0), 32, 4, 2, 1.3, groups=(2, 1), shared=32),
+                     _bare(_lat(2, 16, 16, 16, 32, 24, 20, 0.2, 1000.0)),
+                     _moe(_att(2, 2, 8, 8, 17, 0.5), 16, 2, 1, 0.7)]},
 }
-SEEDS = {"K": 41, "L": 42, "M": 43}
+SEEDS = {"K": 41, "L": 42, "M": 43, "N": 44}
 STDS = {"K": dict(std=0.14, embed_std=0.6, norm_std=0.2, bias_std=0.4), "L": dict(std=0.16, embed_std=0.8, norm_std=0.2, bias_std=0.4),
-        "M": dict(std=0.07, embed_std=0.6, norm_std=0.2, bias_std=0.4)}
-LENGTHS = {"K": [70, 129, 33, 150, 64, 97], "L": [90, 47, 16, 140, 81], "M": [160, 20, 131, 45]}
+        "M": dict(std=0.07, embed_std=0.6, norm_std=0.2, bias_std=0.4), "N": dict(std=0.15, embed_std=0.7, norm_std=0.2, bias_std=0.4)}
+LENGTHS = {"K": [70, 129, 33, 150, 64, 97], "L": [90, 47, 16, 140, 81], "M": [160, 20, 131, 45], "N": [60, 33, 90, 41]}
 
 
 def nat_config(name):

@@ -190,16 +190,16 @@ def forward(cfg, tensors, tokens, dtype=torch.float64, layers_out=None, choices=
     ``choices``: per routed feed-forward that runs, in order, the experts [T, top] to take instead of the router's own;
     ``margins``: a list that receives (the router's own experts, its margins) of every routed feed-forward that runs."""
     t = {k: torch.as_tensor(v).to(dtype) for k, v in tensors.items()}
-    eps, S = cfg["norm"]["eps"], cfg.get("streams", 1)
+    eps, S = cfg["norm"]["eps"], cfg.get("streams")
     x = t["embed"][torch.tensor(tokens)]
-    xs = x[None].repeat(S, 1, 1)
+    xs = x[None].repeat(S or 1, 1, 1)               # without 'streams': one ordinary residual stream
     routed = 0
     for i in layer_order(cfg):
         layer, p = cfg["layers"][i], f"l{i}."
         for q in (1, 2):
             if q == 2 and layer.get("mlp") is None:
                 continue
-            h = rms_norm(hyper_read(xs, t[f"{p}hc{q}.in"]), t[f"{p}norm{q}"], eps)
+            h = rms_norm(xs[0] if S is None else hyper_read(xs, t[f"{p}hc{q}.in"]), t[f"{p}norm{q}"], eps)
             if q == 1:
                 y = mixer(layer["type"], h, _sub(t, p + "mix."), layer["mixer"], eps)
             else:
@@ -207,7 +207,7 @@ def forward(cfg, tensors, tokens, dtype=torch.float64, layers_out=None, choices=
                 routed += 1
                 if margins is not None:
                     margins.append((idx, margin))
-            xs = hyper_write(xs, y, t[f"{p}hc{q}.mix"], t[f"{p}hc{q}.out"])
+            xs = xs + y[None] if S is None else hyper_write(xs, y, t[f"{p}hc{q}.mix"], t[f"{p}hc{q}.out"])
         if layers_out is not None:
             layers_out.append(xs.sum(dim=0))
     return rms_norm(xs.sum(dim=0), t["final.norm"], eps) @ t["head"].T

@@ -120,8 +120,12 @@ def test_to_dict_round_trip_and_keys_that_are_absent():
         assert config_from_dict(cfg.to_dict()) == cfg
     d = copy.deepcopy(NAT["L"])
     assert "loop" not in nat_config("L").to_dict() and nat_config("L").streams == 1
-    d.pop("streams")
-    assert config_from_dict(d).plan().streams == 1
+    d.pop("streams")                                                      # one ordinary residual stream: no hyper-connection weights
+    bare = config_from_dict(d)
+    assert bare.plan().streams == 1 and [l.block for l in bare.plan().layers] == ["pre_norm"] * 4 and "streams" not in bare.to_dict()
+    names = Model(bare.plan(), Runtime(torch.device("cpu"), torch.bfloat16)).tensor_specs()
+    assert "l0.norm1" in names and "l0.norm2" in names and "l1.norm2" not in names and not any(".hc" in n for n in names)
+    assert any(".hc" in n for n in _model("L").tensor_specs())
     d["layers"][2]["mixer"].pop("softcap")                                # a chunked layer without a cap
     assert config_from_dict(d).plan().layers[2].mixer.params["softcap"] is None
 

@@ -444,7 +444,7 @@ def _engine_choices(d, toks):
     return rec
 
 
-@pytest.fixture(scope="module", params=["K", "L", "M"])
+@pytest.fixture(scope="module", params=["K", "L", "M", "N"])
 def nat(request, tmp_path_factory):
     name = request.param
     d = make_nat_dir(tmp_path_factory, name)
@@ -460,7 +460,7 @@ def test_layer_by_layer(nat):
     name, d, plain, reqs, want = nat
     from forge_b200.engine import StepEntry
     runner = make_runner(d, "float32", 256)
-    S, W = NAT[name]["streams"], NAT[name]["width"]
+    S, W = NAT[name].get("streams", 1), NAT[name]["width"]
     sums = []
     for b in set(runner.model.blocks):
         def wrap(orig):
@@ -508,7 +508,7 @@ def test_page_size_and_graphs_do_not_matter(nat, dtype):
 def test_long_decoding_and_first_tokens(nat, dtype):
     """Two tokens, one, then hundreds one by one: windows and chunks pass over decoded tokens, pages fill, follow and go back."""
     name, d, plain, reqs, want = nat
-    n = {"K": 230, "L": 260, "M": 170}[name]
+    n = {"K": 230, "L": 260, "M": 170, "N": 120}[name]
     toks = random_tokens(n, NAT[name]["vocab"], seed=77)
     ref = (plain.forward(toks) if dtype == "float32" else plain.forward_as_routed_in_16_bits(toks)).float()
     runner = make_runner(d, dtype, -(-n // 8) * 8)
