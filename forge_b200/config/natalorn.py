@@ -186,8 +186,8 @@ class NatalornConfig:
     def plan(self) -> ModelPlan:
         W = self.width
 
-        def norm(name):
-            return PartSpec("rmsnorm", {"size": W, "eps": self.norm_eps, "names": {"weight": name}})
+        def norm(name, required=True):
+            return PartSpec("rmsnorm", {"size": W, "eps": self.norm_eps, "names": {"weight": name}, "required": required})
         layers = []
         for i, layer in enumerate(self.layers):
             mlp = layer.get("mlp")
@@ -197,7 +197,8 @@ class NatalornConfig:
                                         weight_prefix=f"l{i}.", norm_prefixes={"input": "", "post_mixer": ""}))
                 continue
             layers.append(LayerSpec(block="hyper_connections", mixer=self._mixer(layer), feed_forward=self._feed_forward(mlp),
-                                    norms={"mixer_in": norm("norm1"), "ff_in": None if mlp is None else norm("norm2")},
+                                    norms={"mixer_in": norm("norm1"), "ff_in": None if mlp is None else norm("norm2"),
+                                           "ff_in_unused": norm("norm2", required=False) if mlp is None else None},
                                     weight_prefix=f"l{i}.", block_params={"streams": self.streams}))
         return ModelPlan(
             hidden_size=W, vocab_size=self.vocab, max_positions=self.max_positions,

@@ -208,6 +208,9 @@ class HyperConnectionBlock(Part):
         self.mixer = build_part("mixer", layer_spec.mixer, rt)
         self.feed_forward = build_part("feed_forward", layer_spec.feed_forward, rt)
         self.norms = {k: None if layer_spec.norms.get(k) is None else build_part("norm", layer_spec.norms[k], rt) for k in ("mixer_in", "ff_in")}
+        # the norm of a feed-forward that the layer does not have: only so that its weight, if a file holds one, has a name
+        spare = layer_spec.norms.get("ff_in_unused")
+        self.spare_norm = None if spare is None else build_part("norm", spare, rt)
         if self.norms["mixer_in"] is None or any(n is not None and type(n) is not RMSNorm for n in self.norms.values()):
             raise ConfigError("a layer on a stream of several copies needs an RMS norm before its mixer (and one before its feed-forward)")
         self.weights = {}
@@ -223,9 +226,13 @@ class HyperConnectionBlock(Part):
         specs = {}
         for part in self._children():
             specs.update(part.tensor_specs())
-        for q in self._sublayers():
-            specs.update({f"hc{q}.in": TensorSpec((S,), role="stream_in"), f"hc{q}.out": TensorSpec((S,), role="stream_in"),
-                          f"hc{q}.mix": TensorSpec((S, S), role="head_mix")})
+        for q in (1, 2):
+            # a layer without a feed-forward has no second sublayer; a file that carries its weights all the same is not refused
+            need = q in self._sublayers()
+            specs.update({f"hc{q}.in": TensorSpec((S,), required=need, role="stream_in"), f"hc{q}.out": TensorSpec((S,), required=need, role="stream_in"),
+                          f"hc{q}.mix": TensorSpec((S, S), required=need, role="head_mix")})
+        if self.norms["ff_in"] is None and self.spare_norm is not None:
+            specs.update(self.spare_norm.tensor_specs())
         return specs
 
     def bind(self, tensors):

@@ -41,7 +41,9 @@ def test_tensor_names_and_shapes():
                         "l1.mix.uk": (24, 20), "l1.mix.uv": (36, 20), "l1.mix.sink": (3,), "l1.mix.g": (36, 80), "l1.mix.o": (80, 36),
                         "l2.mix.q.b": (24,), "l2.mix.k.b": (24,), "l2.mix.v.b": (24,), "l3.mix.k": (10, 80), "l3.mix.v.b": (4,)}.items():
         assert tuple(specs[name].shape) == shape, name
-    assert "l2.norm2" not in specs and "l2.hc2.in" not in specs and "l2.mlp.router" not in specs      # a layer without a feed-forward
+    # a layer without a feed-forward: a file need not hold (but may hold) the second sublayer's norm and stream weights
+    assert not specs["l2.norm2"].required and not specs["l2.hc2.in"].required and not specs["l2.hc2.mix"].required and "l2.mlp.router" not in specs
+    assert specs["l0.norm2"].required and specs["l0.hc2.in"].required
     assert "l0.mix.q.b" not in specs and "l2.mix.o.b" not in specs and "l0.mlp.e6.gate" not in specs
     assert "l3.mlp.shared.gate" not in specs and "l3.mlp.correction" in specs                            # a layer without a shared expert
 

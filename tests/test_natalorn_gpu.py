@@ -479,6 +479,25 @@ def test_layer_by_layer(nat):
         assert max_rel_err(s, ref[i]) <= 2e-5, f"layer run {i}"
 
 
+def test_weights_of_a_sublayer_that_is_not_there_are_let_pass(tmp_path_factory):
+    """A layer without a feed-forward needs no norm and no stream weights for it; a file that holds some loads and computes the same."""
+    from forge_b200.engine import ModelRunner, StepEntry
+    from forge_b200.weights import random_tensors
+    from natalorn_models import nat_config
+    cfg = nat_config("L")
+    tensors = random_tensors(cfg, seed=3, std=0.15, embed_std=0.7)
+    assert "l1.norm2" not in tensors and "l1.hc2.in" not in tensors
+    more = dict(tensors, **{"l1.norm2": torch.ones(48, dtype=torch.bfloat16), "l1.hc2.in": torch.ones(1, dtype=torch.bfloat16),
+                            "l1.hc2.out": torch.ones(1, dtype=torch.bfloat16), "l1.hc2.mix": torch.ones(1, 1, dtype=torch.bfloat16)})
+    toks = random_tokens(40, 130, seed=5)
+    outs = []
+    for t in (tensors, more):
+        runner = ModelRunner(config=cfg, tensors=t, dtype="float32", page_size=8, cache_tokens=64, max_requests=1)
+        runner.admit("x")
+        outs.append(runner.step([StepEntry("x", toks, list(range(40)))]).cpu())
+    assert torch.equal(outs[0], outs[1])
+
+
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("schedule", ["whole", "last_one_by_one", "changing_portions", "mixed"])
 def test_schedules_equal_plain(nat, dtype, schedule):
