@@ -10,8 +10,8 @@ may run several times in a row with the same weights, every pass with a cache of
   "latent_attention"  softmax attention whose keys and values are made per head from one cached latent per token beside one
                       rotated key part that all heads share (channel 2i paired with 2i+1), over a sliding window, with a sink
                       per head in the softmax denominator and a sigmoid gate on the concatenated heads
-  mlp "moe"           routed experts: softmax scores, the choice made by score + correction among the experts of the best groups,
-                      weights = scores times ``router.scale``, not renormalised; a shared expert beside them
+  mlp "moe"           routed experts: softmax scores; ranking by score + correction inside the best-ranked blocks of experts;
+                      weights = the picked scores times ``router.scale`` (their sum is left as it is); a shared expert beside them
 
 config.json keys: ``architecture`` "Natalorn", ``vocab``, ``width``, ``norm.eps``, ``streams``, ``layers`` (per layer ``type``,
 ``mixer`` {sizes and constants}, ``mlp`` {``kind`` "moe", ``expert.ff``, ``router`` {``experts``, ``top``, ``scale``, ``groups``

@@ -415,8 +415,8 @@ extern "C" int forge_head_linear(const void* in, int in_dtype, long long in_ld, 
 extern "C" long long forge_latent_attention_smem(int HG, int C, int R, int TQ, int KT) { return (long long)latent_smem_bytes(HG, C, R, TQ, KT); }
 
 // q [T, H, C+R], out [T, H, C] and cache (rows of C + R) of type dtype.  tile_t0 / tile_n int32 [num_tiles] (both null: one
-// token a tile).  HG: heads per CTA.  window: a position sees the rows of itself and the window - 1 positions before it (0: all);
-// sink fp32 [H] or null: exp(sink_h) joins head h's softmax denominator.
+// token a tile).  HG: heads per CTA.  window: position i reads the rows j with i - window < j <= i (0: every j <= i);
+// sink fp32 [H] or null: exp(sink_h) is added to head h's softmax denominator.
 extern "C" int forge_latent_attention(const void* q, const void* cache, const int32_t* block_table, const int32_t* tok_req,
                                       const int32_t* positions, const int32_t* tile_t0, const int32_t* tile_n, void* out, int dtype,
                                       int num_tiles, int H, int HG, int C, int R, int page_size, int max_pages, float scale, int TQ,

@@ -354,8 +354,8 @@ extern "C" int forge_latent_mma_heads(int H) { return H < BM ? H : BM; }
 
 // q bf16 [T, H*(C+R)]; out bf16 [T, H*C]; u fp32 [nsplit, T, H, C] and part_ml fp32 [nsplit, T, H, 2] (scratch, nsplit > 1: steps of
 // single tokens only).  tile_t0 / tile_n: tiles of consecutive tokens of one request with tile_n * min(H, 64) <= 64 (both null:
-// one token per tile, num_tiles = T).  window: a position sees the rows of itself and the window - 1 positions before it (0: all);
-// sink fp32 [H] or null: exp(sink_h) joins head h's softmax denominator.
+// one token per tile, num_tiles = T).  window: position i reads the rows j with i - window < j <= i (0: every j <= i);
+// sink fp32 [H] or null: exp(sink_h) is added to head h's softmax denominator.
 extern "C" int forge_latent_attention_mma(const void* q, const void* cache, const int32_t* block_table, const int32_t* tok_req,
                                           const int32_t* positions, const int32_t* tile_t0, const int32_t* tile_n, float* u, float* part_ml,
                                           int nsplit, void* out, int T, int num_tiles, int H, int C, int R, int page_size, int max_pages,

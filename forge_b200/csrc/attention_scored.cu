@@ -7,7 +7,7 @@
 //   distance    score(i, j) = scale q(i) . k(j) - r1_h ln(1 + r2_h (i - j))     (r1 = null: no such term)
 //   out_scale   the head outputs are multiplied by it (a mixer that runs beside another one with weights of their own)
 //   window      position i sees j only if i - j < window                              (0: no such limit)
-//   chunk       position i sees j only if floor(i / chunk) = floor(j / chunk)         (0: no such limit)
+//   chunk       position i sees j only if i / chunk == j / chunk (integer division)     (0: no such limit)
 //   softcap     score <- softcap tanh(score / softcap), after the scale                (0: none)
 //
 // and in the prepare step:  an RMS norm over ALL of a token's query channels (and all of its key channels) with a

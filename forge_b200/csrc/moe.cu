@@ -1,10 +1,10 @@
 // A feed-forward made of many small gated feed-forwards ("experts") of which a router picks a few per token.
 //
 //   route       z = Wr x in fp32, score = sigmoid(z) (or softmax over the experts), the `top` largest scores (the lower index
-//               wins a tie) are the token's experts and, as they are or divided by their sum, its weights.  Options: the choice
-//               is made by score + correction_e (the weights stay the scores); the experts form `groups` equal groups of
-//               neighbours, a group counts as its largest choice score, and only experts of the `keep` best groups can be
-//               chosen; the weights are multiplied by a factor
+//               wins a tie) are the token's experts and, as they are or divided by their sum, its weights.  Options: experts are
+//               ranked by score + correction_e (the weights stay the scores); the experts are cut into `groups` consecutive blocks
+//               of equal size, a block is ranked by the largest ranking number in it, and only the `keep` best blocks' experts
+//               take part; the weights are multiplied by a factor
 //   by pairs    every (token, chosen expert) pair on its own: act = act_fn(Wg_e x) * (Wu_e x), then for every token
 //               y = sum over its experts, in the order the router chose them, of weight * Wd_e act.  Everything is read from
 //               device memory, so the path can be replayed in a CUDA graph; it is the path of steps with few tokens
@@ -85,7 +85,7 @@ moe_route_kernel(const TA* __restrict__ x, const float* __restrict__ Wr, int32_t
             for (int e = 0; e < E; ++e) ch[e] = corr ? s[e] + corr[e] : s[e];
         }
         if (groups > 1) {
-            float* gs = ch + E;                      // a group's score: its largest choice score
+            float* gs = ch + E;                      // a block's rank: the largest ranking number in it
             const int per = E / groups;
             for (int g = 0; g < groups; ++g) {
                 float b = -INFINITY;

@@ -988,7 +988,7 @@ def scored_attention(q, cache, group_batch, batch, H, G, M, D, E, page_size, sca
     csrc/attention_scored.cu): scores scale q.k - r1_h ln(1 + r2_h (i - j)); with M = 2 the maps' outputs are combined as
     a1 - lam a2, divided by their root mean square (``eps`` inside the root) and multiplied by ``post``.  Returns [T, H*E] in
     q's type, times ``out_scale``; ``out`` = (matrix, first column): written there instead (the matrix is returned).
-    ``window``: position i sees j only if i - j < window; ``chunk``: only if floor(i / chunk) = floor(j / chunk); ``softcap``: scores
+    ``window``: key j counts for query i only if i - window < j; ``chunk``: only if i // chunk == j // chunk; ``softcap``: scores
     become softcap tanh(score / softcap); 0 switches each off."""
     lib = library("mixers")
     window, chunk, softcap = int(window or 0), int(chunk or 0), float(softcap or 0.0)
@@ -1147,8 +1147,8 @@ def latent_tile_shape(H, C, R, single_tokens=False):
 def latent_attention(q, cache, group_batch, batch, H, C, R, page_size, scale, window=0, sink=None):
     """Causal softmax attention of every token's H absorbed queries (q [T, H*(C+R)]) over its request's latent rows in
     ``cache`` (rows of C + R; the values are a row's first C channels); returns the weighted latents [T, H*C] in q's type.
-    ``window``: a position sees itself and the window - 1 positions before it (0: all); ``sink`` fp32 [H]: exp(sink_h) joins the
-    softmax denominator of head h."""
+    ``window``: position i reads the rows j with i - window < j <= i (0: every j <= i); ``sink`` fp32 [H]: exp(sink_h) is
+    added to the softmax denominator of head h."""
     lib = library("latent")
     window = int(window or 0)
     if sink is not None and sink.numel() != H:
@@ -1197,9 +1197,9 @@ def latent_attention(q, cache, group_batch, batch, H, C, R, page_size, scale, wi
 def moe_route(x, router, top, softmax=False, renorm=False, correction=None, groups=0, keep=0, factor=1.0):
     """(int32 [T, top] experts, fp32 [T, top] weights): the ``top`` largest of sigmoid (or softmax) of router . x per token, the lower
     index winning a tie; the weights are those scores, divided by their sum with ``renorm``, times ``factor``.  router fp32 [E, W];
-    fp32 arithmetic.  ``correction`` fp32 [E]: the choice is made by score + correction (the weights stay the scores).  ``groups``
-    > 1: the experts form that many equal groups of neighbours, a group counts as its largest choice score, and only experts of the
-    ``keep`` best groups can be chosen."""
+    fp32 arithmetic.  ``correction`` fp32 [E]: experts are ranked by score + correction (the weights stay the scores).  ``groups``
+    > 1: the experts are cut into that many consecutive blocks of equal size, a block is ranked by the largest ranking number in it,
+    and only the ``keep`` best blocks' experts take part in the ranking."""
     lib = library("moe")
     T, W = x.shape
     E = router.shape[0]

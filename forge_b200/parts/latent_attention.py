@@ -16,8 +16,8 @@ Wdkv: it reads the rows that the named layer wrote, with matrices of its own.
 The rotation pairs channel 2i with 2i+1; its frequencies (and the factor on cos and sin) come from the position part.
 
 Options, each a constructor parameter: ``window`` (position i sees j only if i - j < window; the rows behind every future query's
-window go back to the pool), ``sink`` (a number per head whose exponential joins the softmax denominator: it has no key and no
-value, is not scaled, and counts once), ``out_gate`` (the concatenated heads are multiplied by sigmoid(Wg h) before Wo; Wg rides
+window go back to the pool), ``sink`` (one learned number per head, b_h: the softmax denominator becomes sum_j exp(score_j) + exp(b_h), as if
+one more key with the unscaled score b_h and a zero value were always visible), ``out_gate`` (the concatenated heads are multiplied by sigmoid(Wg h) before Wo; Wg rides
 in the down-projections' product).
 """
 import torch

@@ -3,9 +3,9 @@
     s = sigmoid(Wr x)  (or softmax(Wr x));   the ``top`` largest s choose the experts (the lower index wins a tie)
     y = sum over the chosen e of s_e * Wdown_e (silu(Wgate_e x) * (Wup_e x))          (s_e divided by their sum with ``renormalize``)
 
-Options: the choice may be made by s + ``correction`` (a number per expert; the weights stay s); the experts may form ``groups``
-equal groups of neighbours of which only the ``keep`` with the largest choice score in them can be chosen from; the weights may be
-multiplied by ``route_scale``; a ``shared`` feed-forward (any feed-forward part) may run for every token and be added.
+Options: experts may be ranked by s + ``correction`` (a number per expert; the weights stay s); the experts may be cut into ``groups``
+consecutive blocks of equal size, each ranked by the largest ranking number in it, of which only the ``keep`` best take part; the weights
+may be multiplied by ``route_scale``; a ``shared`` feed-forward (any feed-forward part) may run for every token and be added.
 
 The router's arithmetic is fp32.  Three paths, all with everything but the last one's row counts read from device memory:
 

@@ -13,7 +13,7 @@ key channels) with a weight per channel; a query temperature 1 + coef ln(floor((
 
 "masked_attention": no rotation (positions do not enter the scores); optional biases in q, k and v; the scale is a parameter;
 optionally  score <- softcap tanh(score / softcap);  and a position i sees j <= i only
-    within a sliding ``window``  (i - j < window),  or  within its own ``chunk``  (floor(i / chunk) = floor(j / chunk)),
+    within a sliding ``window``  (i - window < j),  or  within its own ``chunk``  (i // chunk == j // chunk),
 chunks counted from the sequence's first position.  Pages whose keys no future query sees go back to the pool.
 
 ``out_scale`` multiplies the mixer's output (a mixer that runs beside another with weights of their own).

@@ -115,7 +115,7 @@ def gated_ff(x, w_gate, w_up, w_down):
 
 def route(x, w, r):
     """(chosen experts [T, top], their weights [T, top], margin [T]: how far the choice is from another one, the smaller of the
-    gap between the last chosen and the first not chosen choice score and the gap between the last kept and the first dropped group)."""
+    gap between the last picked and the first passed-over ranking number and the gap between the last kept and the first dropped block)."""
     s = torch.softmax(x @ w["router"].T, dim=-1)
     choice = s + w["correction"]
     n, groups = r["experts"], r.get("groups")

@@ -199,10 +199,10 @@ def test_choice_by_corrected_scores_within_the_best_groups():
     w2 = dict(w, correction=torch.tensor([0, 0, 0, 0, 0, 0, 0, 5.0], dtype=torch.float64))
     idx2, wts2, _ = PN.route(x, w2, r)
     assert bool((idx2[:, 0] == 7).all()) and torch.allclose(wts2[:, 0], 1.5 * s[:, 7])
-    # groups of two of which one is kept: both experts come from the group that holds the best choice score
+    # groups of two of which one is kept: both experts come from the block that holds the best ranking number
     idx3, _, _ = PN.route(x, w, dict(r, groups={"count": 4, "keep": 1}))
     assert bool((idx3[:, 0] // 2 == idx3[:, 1] // 2).all()) and torch.equal(idx3[:, 0], s.argmax(-1))
-    # negative choice scores: an expert outside the kept groups is never taken, although its score is above theirs
+    # negative ranking numbers: an expert outside the kept blocks is never taken, although its score is above theirs
     w4 = dict(w, correction=torch.tensor([-3.0, -3.5, 0, 0, 0, 0, 0, 0], dtype=torch.float64))
     idx4, _, _ = PN.route(x, w4, dict(r, top=4, groups={"count": 4, "keep": 2}))
     assert bool(((idx4 // 2).sort(-1).values[:, 0] == (idx4 // 2).sort(-1).values[:, 1]).all()) and not bool((idx4 < 2).any())

@@ -345,7 +345,7 @@ def test_the_router_chooses_by_corrected_scores_within_the_best_groups():
         assert int(clear.sum()) > T * 0.9
         assert torch.equal(idx.cpu().long()[clear], want_idx[clear]), (E, top, groups, keep)
         assert max_rel_err(wts.cpu()[clear], want_w[clear]) <= 1e-5
-    # negative choice scores: experts of the dropped groups are out although zero would beat the kept ones
+    # negative ranking numbers: experts of the dropped blocks are out although zero would beat the kept ones
     router, corr = torch.zeros(6, 8), torch.tensor([-0.5, -0.9, -0.6, -0.7, -0.8, -0.95])
     idx, wts = kernels.moe_route(torch.ones(2, 8).to(DEV), router.to(DEV), 2, softmax=True, correction=corr.to(DEV), groups=3, keep=1, factor=3.0)
     assert idx.cpu().tolist() == [[0, 1], [0, 1]] and torch.allclose(wts.cpu(), torch.full((2, 2), 0.5))
@@ -392,7 +392,7 @@ class _Plain:
         return PN.forward(self.cfg, self.tensors, list(toks), layers_out=layers_out, margins=margins, choices=choices)
 
     def forward_as_routed_in_16_bits(self, toks):
-        """Where two experts' (or two groups') choice scores lie within the rounding of 16-bit activations, either choice is right
+        """Where two experts' (or two blocks') ranking numbers lie within the rounding of 16-bit activations, either choice is right
         and the outputs differ.  So the 16-bit runtime is compared with the plain implementation taking the experts that the engine
         took for the whole prompt, and every choice that is not the plain router's own must be such a close call."""
         theirs = _engine_choices(self.dir, list(toks))
